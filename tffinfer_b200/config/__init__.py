@@ -2,4 +2,5 @@ from .model_config import (ModelConfig, Qwen3Config, ConfigError, read_config_js
                            FULL_ATTENTION, SLIDING_ATTENTION, architecture_name)
 from .tipezen_config import TipezenConfig, TipezenLayer, RotaryConfig
 from .dominex_config import DominexConfig, DominexLayer, DominexExperts
+from .sadupel_config import SadupelConfig, SadupelLayer, SadupelExperts
 from .engine_config import EngineConfig

@@ -65,7 +65,7 @@ struct AttnParams {
     const bf16* cache; KvLayout L; int layer;
     bf16* out; float* part_o; float* part_ml; int num_splits;
     int nq, nkv; float scale_log2; int window;
-    float scale_over_cap, cap_log2; int sink; const float* gate;   // AttnExtra, ready for the kernel
+    float scale_over_cap, cap_log2; int sink; const float* gate; const float* sink_val;   // AttnExtra, ready for the kernel
 };
 
 template <int D, bool KEYS_MODE>
@@ -285,7 +285,7 @@ attn_fwd_kernel(const AttnParams p) {
             }
             const size_t grow = (size_t)(q0 + R / G) * p.nq + (kvh * G + R % G);
             if (p.num_splits == 1) {
-                if (p.sink) lsum += exp2f(-Ms);                    // the sink: a key of score 0
+                if (p.sink) lsum += exp2f(attn_sink_log2(p.sink_val, kvh * G + R % G) - Ms);   // the sink: a key without a value
                 const float gt = p.gate ? p.gate[grow] : 1.f;
                 p.out[grow * D + c] = __float2bfloat16_rn(acc * gt / lsum);
             } else {
@@ -300,9 +300,9 @@ attn_fwd_kernel(const AttnParams p) {
         const size_t g0 = (size_t)(q0 + R0 / G) * p.nq + (kvh * G + R0 % G);
         const size_t g1 = (size_t)(q0 + R1 / G) * p.nq + (kvh * G + R1 % G);
         if (p.num_splits == 1) {
-            if (p.sink) {                                          // the sink: a key of score 0
-                l0 += exp2f(m0 == -INFINITY ? 0.f : -m0);
-                l1 += exp2f(m1 == -INFINITY ? 0.f : -m1);
+            if (p.sink) {                                          // the sink: a key without a value
+                l0 += exp2f(attn_sink_log2(p.sink_val, kvh * G + R0 % G) - (m0 == -INFINITY ? 0.f : m0));
+                l1 += exp2f(attn_sink_log2(p.sink_val, kvh * G + R1 % G) - (m1 == -INFINITY ? 0.f : m1));
             }
             const float i0 = ((p.gate && v0) ? p.gate[g0] : 1.f) / l0, i1 = ((p.gate && v1) ? p.gate[g1] : 1.f) / l1;
 #pragma unroll
@@ -332,7 +332,7 @@ attn_fwd_kernel(const AttnParams p) {
 // once (two round trips to memory, not two per split)
 template <int D, int MAXS>
 __device__ __forceinline__ void combine_row(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                            bf16* __restrict__ out, int num_splits, size_t row, int sink, float gt) {
+                                            bf16* __restrict__ out, int num_splits, size_t row, int sink, float sink_log2, float gt) {
     float2 ml[MAXS];
 #pragma unroll
     for (int s = 0; s < MAXS; ++s)
@@ -347,7 +347,7 @@ __device__ __forceinline__ void combine_row(const float* __restrict__ part_o, co
         f[s] = (s < num_splits && ml[s].y != 0.f) ? exp2f(ml[s].x - Ms) : 0.f;   // an empty split counts for nothing
         lsum += f[s] * ml[s].y;
     }
-    if (sink) lsum += exp2f(-Ms);                                           // the sink: a key of score 0
+    if (sink) lsum += exp2f(sink_log2 - Ms);                                // the sink: a key without a value
     for (int c = threadIdx.x; c < D; c += blockDim.x) {
         float po[MAXS];
 #pragma unroll
@@ -363,7 +363,8 @@ __device__ __forceinline__ void combine_row(const float* __restrict__ part_o, co
 template <int D>
 __global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     bf16* __restrict__ out, int num_splits, const int* __restrict__ q_start,
-                                    const int* __restrict__ req_ids, int nq, int sink, const float* __restrict__ gate) {
+                                    const int* __restrict__ req_ids, int nq, int sink, const float* __restrict__ gate,
+                                    const float* __restrict__ sink_val) {
     pdl_launch_dependents();          // the next kernel may become resident (it waits before it reads or writes)
     // the step's batch arrays are older than the kernel ahead: they are read before waiting for it
     const int b = req_ids ? req_ids[blockIdx.y] : (int)blockIdx.y;
@@ -374,9 +375,10 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
     if (t >= q_len) return;
     const size_t row = (size_t)(q0 + t) * nq + h;
     const float gt = gate ? gate[row] : 1.f;
-    if (num_splits <= 4) { combine_row<D, 4>(part_o, part_ml, out, num_splits, row, sink, gt); return; }
-    if (num_splits <= 8) { combine_row<D, 8>(part_o, part_ml, out, num_splits, row, sink, gt); return; }
-    if (num_splits <= 16) { combine_row<D, 16>(part_o, part_ml, out, num_splits, row, sink, gt); return; }
+    const float sink_log2 = attn_sink_log2(sink_val, h);
+    if (num_splits <= 4) { combine_row<D, 4>(part_o, part_ml, out, num_splits, row, sink, sink_log2, gt); return; }
+    if (num_splits <= 8) { combine_row<D, 8>(part_o, part_ml, out, num_splits, row, sink, sink_log2, gt); return; }
+    if (num_splits <= 16) { combine_row<D, 16>(part_o, part_ml, out, num_splits, row, sink, sink_log2, gt); return; }
     float M = -INFINITY;
     for (int s = 0; s < num_splits; ++s) M = fmaxf(M, part_ml[(row * num_splits + s) * 2]);
     const float Ms = M == -INFINITY ? 0.f : M;
@@ -389,7 +391,7 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
             acc += f * part_o[(row * num_splits + s) * D + c];
             lsum += f * l;
         }
-        if (sink) lsum += exp2f(-Ms);
+        if (sink) lsum += exp2f(sink_log2 - Ms);
         out[row * D + c] = __float2bfloat16_rn(acc * gt / lsum);
     }
 }
@@ -449,7 +451,7 @@ static int attention_bf16_impl(
     p.window = window;
     p.scale_over_cap = extra.softcap > 0.f ? scale / extra.softcap : 0.f;
     p.cap_log2 = extra.softcap > 0.f ? extra.softcap * 1.4426950408889634f : 0.f;
-    p.sink = extra.sink; p.gate = extra.gate;
+    p.sink = extra.sink; p.gate = extra.gate; p.sink_val = extra.sink_val;
     const bool keys_mode = (long long)max_q_len * G <= 16;
     const int block_m = keys_mode ? 16 : 64;
     const int q_tiles = (max_q_len * G + block_m - 1) / block_m;
@@ -473,10 +475,10 @@ static int attention_bf16_impl(
         const dim3 cgrid((unsigned)(nq * max_q_len), (unsigned)num_requests);
         if (d == 128) return tff_launch_pdl(attn_combine_kernel<128>, cgrid, dim3(128), 0, stream,
                                             (const float*)p.part_o, (const float*)p.part_ml, p.out, num_splits,
-                                            q_start, req_ids, nq, extra.sink, extra.gate);
+                                            q_start, req_ids, nq, extra.sink, extra.gate, extra.sink_val);
         return tff_launch_pdl(attn_combine_kernel<64>, cgrid, dim3(64), 0, stream,
                               (const float*)p.part_o, (const float*)p.part_ml, p.out, num_splits, q_start, req_ids, nq,
-                              extra.sink, extra.gate);
+                              extra.sink, extra.gate, extra.sink_val);
     }
     return TFF_OK;
 }
@@ -488,7 +490,7 @@ TFF_API int tff_attention_bf16(
     int nq, int nkv, int d, float scale, int window, cudaStream_t stream) {
     return attention_bf16_impl(q, q_start, pos_start, nullptr, block_table, table_width, cache, 0, cache_layers, layer,
                                page_size, out, workspace, num_tokens, num_requests, max_q_len, num_splits, nq, nkv, d,
-                               scale, window, AttnExtra{0.f, 0, nullptr}, stream);
+                               scale, window, AttnExtra{0.f, 0, nullptr, nullptr}, stream);
 }
 
 // The same with the number of pages of the cache tensor given, which lets decode-sized calls
@@ -502,7 +504,7 @@ TFF_API int tff_attention_bf16_paged(
     int nq, int nkv, int d, float scale, int window, cudaStream_t stream) {
     return attention_bf16_impl(q, q_start, pos_start, req_ids, block_table, table_width, cache, cache_pages, cache_layers,
                                layer, page_size, out, workspace, num_tokens, num_requests, max_q_len, num_splits, nq,
-                               nkv, d, scale, window, AttnExtra{0.f, 0, nullptr}, stream);
+                               nkv, d, scale, window, AttnExtra{0.f, 0, nullptr, nullptr}, stream);
 }
 
 // The same with a cap on the scores, a sink in the softmax and a multiplier per (token, head) (attention_common.h).
@@ -510,10 +512,10 @@ TFF_API int tff_attention_bf16_paged_ext(
     const void* q, const int* q_start, const int* pos_start, const int* req_ids, const int* block_table, int table_width,
     const void* cache, long long cache_pages, int cache_layers, int layer, int page_size,
     void* out, void* workspace, int num_tokens, int num_requests, int max_q_len, int num_splits,
-    int nq, int nkv, int d, float scale, int window, float softcap, int sink, const float* gate, cudaStream_t stream) {
+    int nq, int nkv, int d, float scale, int window, float softcap, int sink, const float* sink_val, const float* gate, cudaStream_t stream) {
     return attention_bf16_impl(q, q_start, pos_start, req_ids, block_table, table_width, cache, cache_pages, cache_layers,
                                layer, page_size, out, workspace, num_tokens, num_requests, max_q_len, num_splits, nq,
-                               nkv, d, scale, window, AttnExtra{softcap, sink, gate}, stream);
+                               nkv, d, scale, window, AttnExtra{softcap, sink, gate, sink_val}, stream);
 }
 
 // ------------------------------------------------------- allocation-free variant

@@ -4,12 +4,14 @@
 
 // What some designs add to softmax attention; all off = plain attention.
 //   softcap  > 0: a score s (after the scale) becomes softcap * tanh(s / softcap)
-//   sink     != 0: the softmax's denominator has one more term, a key of score 0 that has no value
+//   sink     != 0: the softmax's denominator has one more term, a key that has no value; its score (not scaled, not
+//                 capped) is sink_val[head] (float32 [nq]) or, with sink_val null, 0
 //   gate     float32 [tokens, nq]: the output of head h of token t is multiplied by gate[t, h] (null: by 1)
 struct AttnExtra {
     float softcap;
     int sink;
     const float* gate;
+    const float* sink_val;
 };
 
 #ifdef __CUDACC__
@@ -19,6 +21,10 @@ __device__ __forceinline__ float attn_tanh(float x) {
     float e;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * 2.885390081777927f));
     return 1.0f - __fdividef(2.0f, 1.0f + e);
+}
+// The sink's score of a head in units of log2.
+__device__ __forceinline__ float attn_sink_log2(const float* sink_val, int head) {
+    return sink_val ? sink_val[head] * 1.4426950408889634f : 0.f;
 }
 // A scaled score in units of log2: with a cap, softcap * tanh(s * scale / softcap) * log2(e).
 __device__ __forceinline__ float attn_score_log2(float raw, float scale_log2, float scale_over_cap, float cap_log2) {

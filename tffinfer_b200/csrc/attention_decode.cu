@@ -68,7 +68,7 @@ struct DecodeParams {
     int cache_layers, layer, page_shift;         // page_size = 1 << page_shift
     bf16* out; float* part_o; float* part_ml; int num_splits;
     int nq, nkv; float scale_log2; int window;
-    float scale_over_cap, cap_log2; int sink; const float* gate;   // AttnExtra, ready for the kernel
+    float scale_over_cap, cap_log2; int sink; const float* gate; const float* sink_val;   // AttnExtra, ready for the kernel
     int* error_flag;
 };
 
@@ -324,7 +324,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_cache, const DecodePar
         }
         const size_t grow = (size_t)(q0 + r / G) * p.nq + (kvh * G + r % G);
         if (p.num_splits == 1) {
-            if (p.sink) lsum += exp2f(-Ms);                        // the sink: a key of score 0
+            if (p.sink) lsum += exp2f(attn_sink_log2(p.sink_val, kvh * G + r % G) - Ms);   // the sink: a key without a value
             const float gt = p.gate ? p.gate[grow] : 1.f;
             p.out[grow * D + c] = __float2bfloat16_rn(acc * gt / lsum);
         } else {
@@ -377,7 +377,7 @@ int tff_attention_decode_launch(
     p.nq = nq; p.nkv = nkv; p.scale_log2 = scale * 1.4426950408889634f; p.window = window;
     p.scale_over_cap = extra.softcap > 0.f ? scale / extra.softcap : 0.f;
     p.cap_log2 = extra.softcap > 0.f ? extra.softcap * 1.4426950408889634f : 0.f;
-    p.sink = extra.sink; p.gate = extra.gate;
+    p.sink = extra.sink; p.gate = extra.gate; p.sink_val = extra.sink_val;
     p.error_flag = tff_device_error_flag();
     if (p.error_flag == nullptr) return TFF_ERR_LAUNCH;
     return d == 128 ? launch_decode<128>(tm, p, num_requests, stream) : launch_decode<64>(tm, p, num_requests, stream);

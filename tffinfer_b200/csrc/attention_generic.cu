@@ -12,8 +12,8 @@
 // (paged_flash_attention.cu:696-792) in float32, over key blocks of 32 aligned to
 // absolute positions.  The block boundaries depend on p and the window only, so a
 // token's result does not depend on how the batch was cut or what else is in it.
-// With ``sink`` the softmax has one more term in its denominator, a key of score 0 that has no value:
-// weights exp(s[n]) / (1 + sum exp(s)).  With ``gate`` (float32 [tokens, nq]) the head's output is multiplied by
+// With ``sink`` the softmax has one more term in its denominator, a key that has no value and whose score (neither
+// scaled nor capped) is sink_val[h], or 0 when sink_val is null: weights exp(s[n]) / (exp(sink) + sum exp(s)).  With ``gate`` (float32 [tokens, nq]) the head's output is multiplied by
 // gate[t, h].  Keys have d elements and values dv; both lie in cache slots of dc >= max(d, dv) elements.
 #include "common.cuh"
 
@@ -28,7 +28,8 @@ attention_generic_kernel(const T* __restrict__ q_in, int row_stride,
                          const int* __restrict__ block_table, int table_width,
                          const T* __restrict__ cache, KvLayout L, int layer,
                          T* __restrict__ out, int num_tokens, int nq, int nkv, int d, int dv,
-                         float scale, int window, float softcap, int sink, const float* __restrict__ gate) {
+                         float scale, int window, float softcap, int sink, const float* __restrict__ sink_val,
+                         const float* __restrict__ gate) {
     extern __shared__ float smem[];            // WARPS * d floats: the warp's query row
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long item = (long long)blockIdx.x * WARPS + warp;
@@ -49,8 +50,8 @@ attention_generic_kernel(const T* __restrict__ q_in, int row_stride,
     float o[16];
 #pragma unroll
     for (int j = 0; j < 16; ++j) o[j] = 0.f;
-    // the sink is a key of score 0 ahead of all others: it starts the running maximum and the sum
-    float m = sink ? 0.f : -INFINITY, l = sink ? 1.f : 0.f;
+    // the sink is a key ahead of all others: its score starts the running maximum and the sum
+    float m = sink ? (sink_val ? sink_val[h] : 0.f) : -INFINITY, l = sink ? 1.f : 0.f;
     const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
 
     for (int k0 = (lo / 32) * 32; k0 <= p; k0 += 32) {
@@ -109,7 +110,7 @@ TFF_API int tff_attention_generic_ext(
     const int* positions, const int* tok_req, const int* block_table, int table_width,
     const void* cache, int cache_layers, int layer, int page_size,
     void* out, int num_tokens, int nq, int nkv, int d, int dv, int dc, float scale, int window,
-    float softcap, int sink, const float* gate, cudaStream_t stream) {
+    float softcap, int sink, const float* sink_val, const float* gate, cudaStream_t stream) {
     if (num_tokens <= 0) return TFF_OK;
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || d <= 0 || dv <= 0 || dc < d || dc < dv || page_size <= 0 || softcap < 0.f)
         return TFF_ERR_BAD_ARGUMENT;
@@ -121,11 +122,11 @@ TFF_API int tff_attention_generic_ext(
     if (is_bf16)
         attention_generic_kernel<bf16><<<blocks, WARPS * 32, smem, stream>>>(
             (const bf16*)qkv, row_stride, positions, tok_req, block_table, table_width,
-            (const bf16*)cache, L, layer, (bf16*)out, num_tokens, nq, nkv, d, dv, scale, window, softcap, sink, gate);
+            (const bf16*)cache, L, layer, (bf16*)out, num_tokens, nq, nkv, d, dv, scale, window, softcap, sink, sink_val, gate);
     else
         attention_generic_kernel<float><<<blocks, WARPS * 32, smem, stream>>>(
             (const float*)qkv, row_stride, positions, tok_req, block_table, table_width,
-            (const float*)cache, L, layer, (float*)out, num_tokens, nq, nkv, d, dv, scale, window, softcap, sink, gate);
+            (const float*)cache, L, layer, (float*)out, num_tokens, nq, nkv, d, dv, scale, window, softcap, sink, sink_val, gate);
     return tff_launch_status();
 }
 
@@ -136,5 +137,5 @@ TFF_API int tff_attention_generic(
     void* out, int num_tokens, int nq, int nkv, int d, float scale, int window, cudaStream_t stream) {
     return tff_attention_generic_ext(qkv, is_bf16, row_stride, positions, tok_req, block_table, table_width, cache,
                                      cache_layers, layer, page_size, out, num_tokens, nq, nkv, d, d, d, scale, window,
-                                     0.f, 0, nullptr, stream);
+                                     0.f, 0, nullptr, nullptr, stream);
 }

@@ -166,7 +166,7 @@ struct PrefillParams {
     int cache_layers, layer, page_shift;
     bf16* out;
     int nq, nkv; float scale_log2; int window;
-    float scale_over_cap, cap_log2; int sink; const float* gate;   // AttnExtra, ready for the kernel
+    float scale_over_cap, cap_log2; int sink; const float* gate; const float* sink_val;   // AttnExtra, ready for the kernel
     int* error_flag;
 };
 
@@ -543,7 +543,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const Prefi
         if (ok && nb_x > 0) ok = mbar_wait_warp(pv_done(x, (nb_x - 1) & 1), (uint32_t)((nb_x - 1) >> 1) & 1, abort_flag);
         if (ok && nb_x > 0) {
             tc_fence_after();
-            if (p.sink && l > 0.f) l += exp2f(-m_used);            // the sink: a key of score 0
+            if (p.sink && l > 0.f) l += exp2f(attn_sink_log2(p.sink_val, kvh * G + R % G) - m_used);   // the sink: a key without a value
             float inv = l > 0.f ? 1.f / l : 0.f;
             if (p.gate && rv) inv *= p.gate[(size_t)(q0 + R / G) * p.nq + (kvh * G + R % G)];
             bf16* orow = p.out + ((size_t)(q0 + R / G) * p.nq + (kvh * G + R % G)) * D;
@@ -629,7 +629,7 @@ int tff_attention_prefill_launch(
     p.nq = nq; p.nkv = nkv; p.scale_log2 = scale * 1.4426950408889634f; p.window = window;
     p.scale_over_cap = extra.softcap > 0.f ? scale / extra.softcap : 0.f;
     p.cap_log2 = extra.softcap > 0.f ? extra.softcap * 1.4426950408889634f : 0.f;
-    p.sink = extra.sink; p.gate = extra.gate;
+    p.sink = extra.sink; p.gate = extra.gate; p.sink_val = extra.sink_val;
     p.error_flag = tff_device_error_flag();
     if (p.error_flag == nullptr) return TFF_ERR_LAUNCH;
     const int G = nq / nkv;

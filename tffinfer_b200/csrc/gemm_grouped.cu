@@ -105,6 +105,7 @@ gemm_grouped_kernel(const TA* __restrict__ A, long long lda, long long a_gs,
             if (n >= N) continue;
             float v = acc[i][j];
             if constexpr (GATED) v = act_apply(v, act) * acc2[i][j];
+            else if (act == 2) { v = fmaxf(v, 0.f); v = v * v; }     // a plain product with the square of relu behind it
             crow[n] = from_f32<TCc>(v);
         }
     }
@@ -112,7 +113,8 @@ gemm_grouped_kernel(const TA* __restrict__ A, long long lda, long long a_gs,
 
 }  // namespace
 
-// dt codes: 0 = float32, 1 = bfloat16.  B2 null = plain product; else gated with ``act`` (0 silu, 1 tanh-gelu).
+// dt codes: 0 = float32, 1 = bfloat16.  B2 null = plain product (``act`` 2: relu(.)^2 of it; else as it is); else gated
+// with ``act`` (0 silu, 1 tanh-gelu).
 // b_interleaved (gated only) > 0: the gate and up rows of a group alternate in blocks of that many rows in ONE matrix
 // (B2 = B + that many rows); 0: B and B2 are matrices of their own.
 // Uniform: tile_group null, ``groups`` groups of M rows.  Ragged: the four tile arrays on the device, ``max_tiles`` the

@@ -146,7 +146,11 @@ gemm_grouped_mma_kernel(const bf16* __restrict__ A, long long lda, long long a_g
                     const int n = n0 + wn * 64 + nj * 8 + 2 * (lane & 3);
 #pragma unroll
                     for (int e = 0; e < 2; ++e)
-                        if (n + e < N) crow[n + e] = from_f32<TCc>(acc[mi][nj][half * 2 + e]);
+                        if (n + e < N) {
+                            float v = acc[mi][nj][half * 2 + e];
+                            if (act == 2) { v = fmaxf(v, 0.f); v = v * v; }     // the square of relu behind a plain product
+                            crow[n + e] = from_f32<TCc>(v);
+                        }
                 }
             }
         }

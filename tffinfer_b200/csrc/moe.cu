@@ -1,8 +1,12 @@
 // The small kernels around a routed feed-forward (mixture of experts); the experts' products are gemm_grouped.cu.
 //
-//   route    per token: z = W_r h in float32 (one warp per expert, a fixed order of additions), s = sigmoid(z), the
-//            ``top`` experts of largest s (the lower index wins a tie), optionally renormalised to sum 1; writes the
-//            pair (token, k) -> (expert, weight) and counts the pairs of every expert
+//   route    per token: z = W_r h in float32 (one warp per expert, a fixed order of additions), s = sigmoid(z) or
+//            softmax(z) over all outputs, choice scores s + correction, optionally only the experts of the best
+//            ``keep`` of ``groups`` groups of neighbours (a group's score is its best choice score), the ``top`` experts
+//            of largest choice score (the lower index wins a tie), weights s, optionally renormalised to sum 1; writes
+//            the pair (token, k) -> (expert, weight) and counts the pairs of every expert.  The last router outputs may
+//            be identity experts (output = weight * input): their pairs get expert -1, no row in the experts' products,
+//            and the combine kernel adds them from the input rows
 //   plan     one block: the experts' row ranges in the sorted order, the tile table of the grouped product (tiles of
 //            ``tile_rows`` rows that never span two experts), and the counters back to zero for the next call
 //   gather   per pair: its place among its expert's rows (an atomic cursor: the order within an expert is not fixed,
@@ -17,10 +21,13 @@ namespace {
 template <typename TH, typename TW>
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const TH* __restrict__ h, const TW* __restrict__ w_router, int W, int E, int top, int renormalize,
+                 int softmax_scores, const float* __restrict__ correction, int groups, int keep, int num_real,
                  int* __restrict__ pair_expert, float* __restrict__ pair_weight, int* __restrict__ counts) {
-    extern __shared__ float sm[];              // W floats: the token's row; E floats: the scores
+    extern __shared__ float sm[];              // W floats: the token's row; E: the scores; E: the choice scores; E: groups
     float* row = sm;
     float* score = sm + W;
+    float* choice = score + E;
+    float* gbest = choice + E;
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -31,15 +38,55 @@ moe_route_kernel(const TH* __restrict__ h, const TW* __restrict__ w_router, int 
         float acc = 0.f;
         for (int i = lane; i < W; i += 32) acc = fmaf(row[i], to_f32<TW>(wr[i]), acc);
         acc = warp_sum(acc);
-        if (lane == 0) score[e] = 1.0f / (1.0f + expf(-acc));
+        if (lane == 0) score[e] = softmax_scores ? acc : 1.0f / (1.0f + expf(-acc));
     }
     __syncthreads();
     if (warp != 0) return;
+    if (softmax_scores) {                      // over all router outputs, in an order that E alone fixes
+        float m = -INFINITY;
+        for (int e = lane; e < E; e += 32) m = fmaxf(m, score[e]);
+        m = warp_max(m);
+        float sum = 0.f;
+        for (int e = lane; e < E; e += 32) { const float x = expf(score[e] - m); score[e] = x; sum += x; }
+        sum = warp_sum(sum);
+        __syncwarp();
+        for (int e = lane; e < E; e += 32) score[e] = score[e] / sum;
+        __syncwarp();
+    }
+    for (int e = lane; e < E; e += 32) choice[e] = score[e] + (correction ? correction[e] : 0.f);
+    __syncwarp();
+    if (groups > 1 && keep < groups) {         // only the experts of the ``keep`` groups with the best member stay
+        const int per = E / groups;
+        for (int g = lane; g < groups; g += 32) {
+            float b = -INFINITY;
+            for (int j = 0; j < per; ++j) b = fmaxf(b, choice[g * per + j]);
+            gbest[g] = b;
+        }
+        __syncwarp();
+        for (int k = 0; k < keep; ++k) {
+            float best = -INFINITY; int arg = 0x7fffffff;
+            for (int g = lane; g < groups; g += 32) {
+                const float s = gbest[g];
+                if (!isnan(s) && (arg == 0x7fffffff || s > best)) { best = s; arg = g; }   // kept groups are NaN
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+                if (oa != 0x7fffffff && (arg == 0x7fffffff || ob > best || (ob == best && oa < arg))) { best = ob; arg = oa; }
+            }
+            if (lane == 0 && arg != 0x7fffffff) gbest[arg] = __int_as_float(0x7fc00000);   // NaN marks a kept group
+            __syncwarp();
+        }
+        for (int e = lane; e < E; e += 32)
+            if (!isnan(gbest[e / per])) choice[e] = -INFINITY;
+        __syncwarp();
+    }
     float total = 0.f;
     for (int k = 0; k < top; ++k) {
-        float best = -1.f; int arg = 0x7fffffff;
+        float best = -INFINITY; int arg = 0x7fffffff;
         for (int e = lane; e < E; e += 32) {
-            const float s = score[e];
+            const float s = choice[e];
             if (s > best) { best = s; arg = e; }      // ascending e: the first of equals stays
         }
 #pragma unroll
@@ -48,13 +95,17 @@ moe_route_kernel(const TH* __restrict__ h, const TW* __restrict__ w_router, int 
             const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
             if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
         }
+        const float wgt = arg != 0x7fffffff ? score[arg] : 0.f;   // the weight is the score without the correction
         if (lane == 0) {
-            pair_expert[(size_t)t * top + k] = arg;
-            pair_weight[(size_t)t * top + k] = best;
-            atomicAdd(&counts[arg], 1);
-            score[arg] = -2.f;                        // taken
+            // an identity expert (index >= num_real) has no rows among the experts' products: -1
+            pair_expert[(size_t)t * top + k] = (arg == 0x7fffffff || arg >= num_real) ? -1 : arg;
+            pair_weight[(size_t)t * top + k] = wgt;
+            if (arg != 0x7fffffff) {
+                if (arg < num_real) atomicAdd(&counts[arg], 1);
+                choice[arg] = -INFINITY;              // taken
+            }
         }
-        total += best;
+        total += wgt;
         __syncwarp();
     }
     if (renormalize && lane == 0)
@@ -97,8 +148,13 @@ moe_gather_kernel(const TH* __restrict__ h, int W, int top, const int* __restric
     pdl_launch_dependents();
     pdl_wait();
     const int pair = blockIdx.x;
+    const int expert = pair_expert[pair];
+    if (expert < 0) {                                 // an identity expert: no row among the experts' products
+        if (threadIdx.x == 0 && place_of_pair) place_of_pair[pair] = -1;
+        return;
+    }
     if (threadIdx.x == 0) {
-        place_s = atomicAdd(&cursor[pair_expert[pair]], 1);
+        place_s = atomicAdd(&cursor[expert], 1);
         row_map[place_s] = pair;
         if (place_of_pair) place_of_pair[pair] = place_s;
     }
@@ -110,10 +166,11 @@ moe_gather_kernel(const TH* __restrict__ h, int W, int top, const int* __restric
     for (int i = threadIdx.x; i < W; i += 128) dst[i] = from_f32<TH>(w * to_f32<TH>(src[i]));
 }
 
+template <typename TH>
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ y, int W, int top, const float* __restrict__ pair_weight,
                    int weight_on_output, const int* __restrict__ place_of_pair, float* __restrict__ residual,
-                   float* __restrict__ out) {
+                   float* __restrict__ out, const int* __restrict__ pair_expert, const TH* __restrict__ h) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
@@ -121,8 +178,12 @@ moe_combine_kernel(const float* __restrict__ y, int W, int top, const float* __r
     if (i >= W) return;
     float acc = 0.f;
     for (int k = 0; k < top; ++k) {
-        const float w = weight_on_output ? pair_weight[(size_t)t * top + k] : 1.f;
         const size_t pair = (size_t)t * top + k;              // y in (token, rank) order, or in the sorted order
+        if (pair_expert && pair_expert[pair] < 0) {           // an identity expert: the weight times the input itself
+            acc = fmaf(pair_weight[pair], to_f32<TH>(h[(size_t)t * W + i]), acc);
+            continue;
+        }
+        const float w = weight_on_output ? pair_weight[pair] : 1.f;
         acc = fmaf(w, y[(place_of_pair ? (size_t)place_of_pair[pair] : pair) * W + i], acc);
     }
     const size_t at = (size_t)t * W + i;
@@ -131,18 +192,26 @@ moe_combine_kernel(const float* __restrict__ y, int W, int top, const float* __r
 
 }  // namespace
 
+// E router outputs, of which the last E - num_real are identity experts (pair_expert -1).  softmax_scores: the scores are
+// softmax(z) over all E outputs instead of sigmoid(z).  correction [E] float32 or null: added to the scores for the
+// choice only.  groups > 1 with keep < groups: E / groups neighbours form a group, and only the ``keep`` groups whose best
+// choice score is largest can be chosen from.
 TFF_API int tff_moe_route(const void* h, int h_dt, const void* w_router, int w_dt, int T, int W, int E, int top,
-                          int renormalize, int* pair_expert, float* pair_weight, int* counts, cudaStream_t stream) {
+                          int renormalize, int softmax_scores, const float* correction, int groups, int keep,
+                          int num_real, int* pair_expert, float* pair_weight, int* counts, cudaStream_t stream) {
     if (T <= 0) return TFF_OK;
-    if (W <= 0 || E <= 0 || top <= 0 || top > E || !h || !w_router) return TFF_ERR_BAD_ARGUMENT;
-    const size_t smem = (size_t)(W + E) * sizeof(float);
+    if (W <= 0 || E <= 0 || top <= 0 || top > E || !h || !w_router || num_real < 0 || num_real > E)
+        return TFF_ERR_BAD_ARGUMENT;
+    if (groups > 1 && (E % groups != 0 || keep <= 0 || keep > groups || top > keep * (E / groups))) return TFF_ERR_BAD_ARGUMENT;
+    const size_t smem = (size_t)(W + 3 * E) * sizeof(float);
     if (smem > 200 * 1024) return TFF_ERR_UNSUPPORTED;
 #define TFF_ROUTE(TH, TW)                                                                                             \
     do {                                                                                                              \
         if (smem > 48 * 1024)                                                                                         \
             cudaFuncSetAttribute(moe_route_kernel<TH, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
         return tff_launch_pdl(moe_route_kernel<TH, TW>, dim3(T), dim3(128), smem, stream, (const TH*)h,               \
-                              (const TW*)w_router, W, E, top, renormalize, pair_expert, pair_weight, counts);         \
+                              (const TW*)w_router, W, E, top, renormalize, softmax_scores, correction, groups, keep, \
+                              num_real, pair_expert, pair_weight, counts);         \
     } while (0)
     if (h_dt == 0 && w_dt == 0) TFF_ROUTE(float, float);
     if (h_dt == 0 && w_dt == 1) TFF_ROUTE(float, bf16);
@@ -172,10 +241,17 @@ TFF_API int tff_moe_gather(const void* h, int h_dt, int pairs, int W, int top, c
                           pair_expert, pair_weight, weight_on_input, cursor, row_map, place_of_pair, (bf16*)x);
 }
 
+// pair_expert (null: every pair has a row in y) and h [T, W] (h_dt 0 float32, 1 bfloat16): pairs whose expert is -1 are
+// identity experts and add pair_weight * h[t]; pair_weight must then be given.
 TFF_API int tff_moe_combine(const float* y, int T, int W, int top, const float* pair_weight, int weight_on_output,
-                            const int* place_of_pair, float* residual, float* out, cudaStream_t stream) {
+                            const int* place_of_pair, float* residual, float* out, const int* pair_expert,
+                            const void* h, int h_dt, cudaStream_t stream) {
     if (T <= 0) return TFF_OK;
+    if (pair_expert && (!h || !pair_weight)) return TFF_ERR_BAD_ARGUMENT;
     dim3 grid(T, (W + 255) / 256);
-    return tff_launch_pdl(moe_combine_kernel, grid, dim3(256), 0, stream, y, W, top, pair_weight, weight_on_output,
-                          place_of_pair, residual, out);
+    if (h_dt == 1)
+        return tff_launch_pdl(moe_combine_kernel<bf16>, grid, dim3(256), 0, stream, y, W, top, pair_weight, weight_on_output,
+                              place_of_pair, residual, out, pair_expert, (const bf16*)h);
+    return tff_launch_pdl(moe_combine_kernel<float>, grid, dim3(256), 0, stream, y, W, top, pair_weight, weight_on_output,
+                          place_of_pair, residual, out, pair_expert, (const float*)h);
 }

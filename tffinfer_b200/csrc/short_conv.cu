@@ -1,0 +1,209 @@
+// A short causal convolution over time on the channels of a merged projection, with the RMS norm of whole column
+// segments behind it, and the per-request state that carries the convolution across steps.
+//
+//   proj[t] = [seg 0 | seg 1 | seg 2 | rest]      float32 rows of the step's tokens (a product's accumulators)
+//   y[t, c] = sum_j w[c, j] * u[t - (taps - 1) + j, c]       j = 0 .. taps-1, u = proj, zeros before position 0
+//   out[t, seg] = y[t, seg] / sqrt(mean(y[t, seg]^2) + eps) * g_seg        for segments that have a norm weight
+//   out[t, rest] = proj[t, rest]
+//
+// The taps-1 rows of u that precede a request's first token of this step come from state[slot] ([taps-1, C] float32,
+// C = the segments' channels together, the oldest row first); a request whose first token is at position 0 reads
+// zeros instead.  The engine clears a slot when position 0 arrives, so both are the same; the kernel does not rely
+// on it.  A second kernel, launched behind the first, leaves the request's last taps-1 rows of u in the slot and,
+// where the rows are an accumulator buffer that is kept at zero between uses, clears them.
+// Sums of squares are added in an order that depends on the row's width alone.
+#include "common.cuh"
+
+namespace {
+
+constexpr int MAX_SEGS = 3;
+constexpr int MAX_TAPS = 8;
+
+struct ConvSegs {
+    int n;
+    int off[MAX_SEGS];            // first column of the segment in a row of proj / out and in a row of the state
+    int width[MAX_SEGS];
+    const float* w[MAX_SEGS];     // [width, taps] or null: the segment passes as it is
+    const float* norm[MAX_SEGS];  // [width] or null: no norm
+};
+
+__global__ void __launch_bounds__(256)
+short_conv_norm_kernel(const float* __restrict__ proj, int ld, float* __restrict__ out, ConvSegs segs, int taps, int C,
+                       const float* __restrict__ state, const int* __restrict__ positions,
+                       const int* __restrict__ tok_req, const int* __restrict__ q_start,
+                       const int* __restrict__ slots, float eps) {
+    __shared__ float red[32];
+    const int t = blockIdx.x;
+    const int b = tok_req[t];
+    const int pos = positions[t];
+    const int i_in = t - q_start[b];                       // the token's place in its request's portion
+    const float* st = state + (size_t)slots[b] * (taps - 1) * C;
+    for (int s = 0; s < segs.n; ++s) {
+        const int off = segs.off[s], width = segs.width[s];
+        float ss = 0.f;
+        for (int c = threadIdx.x; c < width; c += 256) {
+            float y;
+            if (segs.w[s]) {
+                y = 0.f;
+                const float* wc = segs.w[s] + (size_t)c * taps;
+                for (int j = 0; j < taps; ++j) {
+                    const int back = taps - 1 - j;           // how many tokens before this one
+                    if (back > pos) continue;                // before the sequence's start
+                    float u;
+                    if (back <= i_in) u = proj[(size_t)(t - back) * ld + off + c];
+                    else u = st[(size_t)(taps - 1 - (back - i_in)) * C + off + c];
+                    y = fmaf(wc[j], u, y);
+                }
+            } else {
+                y = proj[(size_t)t * ld + off + c];
+            }
+            out[(size_t)t * ld + off + c] = y;
+            ss = fmaf(y, y, ss);
+        }
+        if (segs.norm[s]) {                                  // uniform over the block
+            ss = block_sum<256>(ss, red);
+            const float rs = rsqrtf(ss / (float)width + eps);
+            for (int c = threadIdx.x; c < width; c += 256)   // a thread reads back what it wrote itself
+                out[(size_t)t * ld + off + c] = (out[(size_t)t * ld + off + c] * rs) * segs.norm[s][c];
+            __syncthreads();                                 // red is used again
+        }
+    }
+    for (int c = C + threadIdx.x; c < ld; c += 256) out[(size_t)t * ld + c] = proj[(size_t)t * ld + c];
+}
+
+// grid (requests, column blocks of 256).  A thread owns one column of one request: it moves the state up by the
+// portion's length (oldest first, so nothing is overwritten before it is read), fills the rest from the portion's last
+// rows, and clears the portion's rows of that column when asked to.
+__global__ void __launch_bounds__(256)
+short_conv_state_kernel(float* __restrict__ proj, int ld, int clear, int taps, int C, float* __restrict__ state,
+                        const int* __restrict__ q_start, const int* __restrict__ pos_start,
+                        const int* __restrict__ slots) {
+    const int b = blockIdx.x;
+    const int c = blockIdx.y * 256 + threadIdx.x;
+    if (c >= ld) return;
+    const int q0 = q_start[b], n = q_start[b + 1] - q0;
+    if (c < C && n > 0) {
+        float* st = state + (size_t)slots[b] * (taps - 1) * C + c;
+        const bool fresh = pos_start[b] == 0;
+        for (int s = 0; s < taps - 1; ++s) {
+            const int i = n - (taps - 1) + s;               // the row of the portion that ends up at place s
+            float v;
+            if (i >= 0) v = proj[(size_t)(q0 + i) * ld + c];
+            else v = fresh ? 0.f : st[(size_t)(s + n) * C];
+            st[(size_t)s * C] = v;
+        }
+    }
+    if (clear)
+        for (int i = 0; i < n; ++i) proj[(size_t)(q0 + i) * ld + c] = 0.f;
+}
+
+// x[t, k, :] += table[row(t), :] for every copy k, with row(t) = (prev * mul_prev + tok * mul_cur) mod buckets, prev
+// the token before t in its request (from the step's tokens, or from state[slot] for a portion's first token), and
+// row ``buckets`` for a request's token at position 0.
+template <typename TW>
+__global__ void __launch_bounds__(128)
+pair_embed_kernel(const int* __restrict__ tokens, const int* __restrict__ positions, const int* __restrict__ tok_req,
+                  const int* __restrict__ q_start, const int* __restrict__ slots, const int* __restrict__ state,
+                  const TW* __restrict__ table, int buckets, long long mul_prev, long long mul_cur,
+                  float* __restrict__ x, int copies, int W) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int b = tok_req[t];
+    long long row = buckets;
+    if (positions[t] > 0) {
+        const long long prev = t > q_start[b] ? tokens[t - 1] : state[slots[b]];
+        row = (prev * mul_prev + (long long)tokens[t] * mul_cur) % buckets;
+        if (row < 0) row += buckets;
+    }
+    const TW* src = table + (size_t)row * W;
+    float* dst = x + (size_t)t * copies * W;
+    for (int i = threadIdx.x; i < W; i += 128) {
+        const float v = to_f32<TW>(src[i]);
+        for (int k = 0; k < copies; ++k) dst[(size_t)k * W + i] += v;
+    }
+}
+
+__global__ void last_token_kernel(const int* __restrict__ tokens, const int* __restrict__ q_start,
+                                  const int* __restrict__ slots, int* __restrict__ state, int num_requests) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= num_requests) return;
+    const int q1 = q_start[b + 1];
+    if (q1 > q_start[b]) state[slots[b]] = tokens[q1 - 1];
+}
+
+// y = act(x) elementwise: 2 = the square of relu.
+template <typename T>
+__global__ void unary_act_kernel(const T* __restrict__ x, T* __restrict__ y, long long n, int act) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float v = to_f32<T>(x[i]);
+    if (act == 2) { v = fmaxf(v, 0.f); v = v * v; }
+    y[i] = from_f32<T>(v);
+}
+
+}  // namespace
+
+// seg_off / seg_width / seg_w / seg_norm: arrays of num_segs (<= 3) entries; the segments lie one behind the other
+// from column 0 and their widths add up to C <= ld.  state [slots, taps-1, C] float32.
+TFF_API int tff_short_conv_norm(const float* proj, int ld, float* out, int num_segs, const int* seg_width,
+                                const float* const* seg_w, const float* const* seg_norm, int taps, float eps,
+                                const float* state, const int* positions, const int* tok_req, const int* q_start,
+                                const int* slots, int num_tokens, cudaStream_t stream) {
+    if (num_tokens <= 0) return TFF_OK;
+    if (!proj || !out || num_segs <= 0 || num_segs > MAX_SEGS || taps < 1 || taps > MAX_TAPS) return TFF_ERR_BAD_ARGUMENT;
+    ConvSegs segs;
+    segs.n = num_segs;
+    int C = 0;
+    for (int s = 0; s < MAX_SEGS; ++s) {
+        segs.off[s] = C;
+        segs.width[s] = s < num_segs ? seg_width[s] : 0;
+        segs.w[s] = s < num_segs ? seg_w[s] : nullptr;
+        segs.norm[s] = s < num_segs ? seg_norm[s] : nullptr;
+        if (s < num_segs && seg_width[s] <= 0) return TFF_ERR_BAD_ARGUMENT;
+        C += segs.width[s];
+    }
+    if (C > ld || (taps > 1 && !state)) return TFF_ERR_BAD_ARGUMENT;
+    short_conv_norm_kernel<<<num_tokens, 256, 0, stream>>>(proj, ld, out, segs, taps, C, state, positions, tok_req,
+                                                           q_start, slots, eps);
+    return tff_launch_status();
+}
+
+TFF_API int tff_short_conv_state(float* proj, int ld, int clear, int taps, int C, float* state, const int* q_start,
+                                 const int* pos_start, const int* slots, int num_requests, cudaStream_t stream) {
+    if (num_requests <= 0 || (taps <= 1 && !clear)) return TFF_OK;
+    if (!proj || C > ld || taps > MAX_TAPS || (taps > 1 && !state)) return TFF_ERR_BAD_ARGUMENT;
+    dim3 grid(num_requests, (ld + 255) / 256);
+    short_conv_state_kernel<<<grid, 256, 0, stream>>>(proj, ld, clear, taps, taps > 1 ? C : 0, state, q_start, pos_start, slots);
+    return tff_launch_status();
+}
+
+TFF_API int tff_pair_embed(const int* tokens, const int* positions, const int* tok_req, const int* q_start,
+                           const int* slots, int* state, const void* table, int table_is_bf16, int buckets,
+                           long long mul_prev, long long mul_cur, float* x, int copies, int W, int num_tokens,
+                           int num_requests, cudaStream_t stream) {
+    if (num_tokens <= 0) return TFF_OK;
+    if (!state || !table || !x || buckets <= 0 || copies <= 0 || W <= 0) return TFF_ERR_BAD_ARGUMENT;
+    int st;
+    if (table_is_bf16)
+        st = tff_launch_pdl(pair_embed_kernel<bf16>, dim3(num_tokens), dim3(128), 0, stream, tokens, positions, tok_req,
+                            q_start, slots, (const int*)state, (const bf16*)table, buckets, mul_prev, mul_cur, x, copies, W);
+    else
+        st = tff_launch_pdl(pair_embed_kernel<float>, dim3(num_tokens), dim3(128), 0, stream, tokens, positions, tok_req,
+                            q_start, slots, (const int*)state, (const float*)table, buckets, mul_prev, mul_cur, x, copies, W);
+    if (st != TFF_OK) return st;
+    return tff_launch_pdl(last_token_kernel, dim3((num_requests + 127) / 128), dim3(128), 0, stream, tokens, q_start,
+                          slots, state, num_requests);
+}
+
+TFF_API int tff_unary_act(const void* x, void* y, int is_bf16, long long n, int act, cudaStream_t stream) {
+    if (n <= 0) return TFF_OK;
+    if (act != 2) return TFF_ERR_BAD_ARGUMENT;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (is_bf16) return tff_launch_pdl(unary_act_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16*)x, (bf16*)y, n, act);
+    return tff_launch_pdl(unary_act_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)x, (float*)y, n, act);
+}

@@ -39,7 +39,8 @@ stream_step_kernel(float* __restrict__ x, int S, int W,
                    float* __restrict__ y, int clear_y, const float* __restrict__ scale,
                    const float* __restrict__ mix, const float* __restrict__ outw,
                    const float* __restrict__ inw, const float* __restrict__ w, float eps,
-                   const int* __restrict__ row_index, TO* __restrict__ h, float* __restrict__ total) {
+                   const int* __restrict__ row_index, TO* __restrict__ h, float* __restrict__ total,
+                   const float* __restrict__ bias) {
     extern __shared__ __align__(16) float u_row[];   // W floats: the combined row, kept between the two passes
     __shared__ float red[32];
     __shared__ float c_mix[MAX_STREAMS * MAX_STREAMS], c_out[MAX_STREAMS], c_in[MAX_STREAMS];
@@ -62,7 +63,7 @@ stream_step_kernel(float* __restrict__ x, int S, int W,
     // four columns a thread at a time (16-byte accesses) when the rows allow it; which path runs depends on W and
     // the buffers' alignment alone, so a row's sums are always added in the same order
     const bool vec = MAX_STREAMS <= 8 && (W & 3) == 0 &&
-                     (((uintptr_t)x | (uintptr_t)y | (uintptr_t)scale | (uintptr_t)total) & 15) == 0;
+                     (((uintptr_t)x | (uintptr_t)y | (uintptr_t)scale | (uintptr_t)total | (uintptr_t)bias) & 15) == 0;
     if (vec) {
         const int W4 = W >> 2;
         for (int i = threadIdx.x; i < W4; i += NT) {
@@ -93,7 +94,16 @@ stream_step_kernel(float* __restrict__ x, int S, int W,
                 }
 #pragma unroll
                 for (int t = 0; t < MAX_STREAMS; ++t)
-                    if (t < S) { v[t] = n[t]; if (store_x) reinterpret_cast<float4*>(xr + (size_t)t * W)[i] = n[t]; }
+                    if (t < S) { v[t] = n[t]; if (store_x && !bias) reinterpret_cast<float4*>(xr + (size_t)t * W)[i] = n[t]; }
+            }
+            if (bias) {                               // a vector added to every stream, behind the write
+                const float4 bv = reinterpret_cast<const float4*>(bias)[i];
+#pragma unroll
+                for (int t = 0; t < MAX_STREAMS; ++t)
+                    if (t < S) {
+                        v[t].x += bv.x; v[t].y += bv.y; v[t].z += bv.z; v[t].w += bv.w;
+                        if (store_x) reinterpret_cast<float4*>(xr + (size_t)t * W)[i] = v[t];
+                    }
             }
             if (h || total) {
                 float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -143,7 +153,11 @@ stream_step_kernel(float* __restrict__ x, int S, int W,
                 n[t] = t < S ? fmaf(c_out[t], ys, a) : 0.f;
             }
 #pragma unroll
-            for (int t = 0; t < MAX_STREAMS; ++t) if (t < S) { v[t] = n[t]; if (store_x) xr[(size_t)t * W + i] = n[t]; }
+            for (int t = 0; t < MAX_STREAMS; ++t) if (t < S) { v[t] = n[t]; if (store_x && !bias) xr[(size_t)t * W + i] = n[t]; }
+        }
+        if (bias) {
+#pragma unroll
+            for (int t = 0; t < MAX_STREAMS; ++t) if (t < S) { v[t] += bias[i]; if (store_x) xr[(size_t)t * W + i] = v[t]; }
         }
         if (h || total) {
             float u = 0.f;
@@ -186,10 +200,10 @@ __global__ void embed_streams_kernel(const int* __restrict__ tokens, const TW* _
 // x [rows_total, S, W] float32 (updated in place when y is given); y [rows_total, W] float32 or null;
 // h [rows, W] of the activation type or null; total [rows, W] float32 or null (the combined row itself).
 // clear_y != 0: the rows of y that were read are set to zero (y is then an accumulator buffer that the next split
-// product adds into).
+// product adds into).  bias [W] float32 or null: added to every stream behind the write, ahead of the read.
 TFF_API int tff_stream_step(float* x, int S, int W, float* y, int clear_y, const float* scale, const float* mix,
                             const float* outw, const float* inw, const float* w, float eps, const int* row_index,
-                            void* h, int h_is_bf16, float* total, int rows, cudaStream_t stream) {
+                            void* h, int h_is_bf16, float* total, int rows, const float* bias, cudaStream_t stream) {
     if (rows <= 0) return TFF_OK;
     if (!x || S <= 0 || W <= 0) return TFF_ERR_BAD_ARGUMENT;
     if (S > MOST_STREAMS) return TFF_ERR_UNSUPPORTED;
@@ -213,7 +227,7 @@ TFF_API int tff_stream_step(float* x, int S, int W, float* y, int clear_y, const
             }                                                                                                  \
         }                                                                                                      \
         return tff_launch_pdl(kern, dim3(rows), dim3(NT), smem, stream, x, S, W, y, clear_y, scale, mix, outw, inw, w, \
-                              eps, row_index, (TO*)h, total);                                                  \
+                              eps, row_index, (TO*)h, total, bias);                                                  \
     } while (0)
     if (W >= 1024) {
         if (h_is_bf16) TFF_STREAM_LAUNCH(bf16, 256);

@@ -107,6 +107,10 @@ class ModelRunner:
                 elif isinstance(one, StateNeed):
                     self.bindings[e].state_index = len(state_specs)
                     state_specs.append(one)
+        for i, one in enumerate(self.model.extra_state_needs()):      # what parts of the embedding keep per request
+            if isinstance(one, StateNeed):
+                self.model.embed_state_index[i] = len(state_specs)
+                state_specs.append(one)
         for e, entry in enumerate(self.desc.schedule):
             if entry.cache_of is not None:
                 src = self.bindings[entry.cache_of]

@@ -408,7 +408,7 @@ class CudaKernels:
     def _foldable_weight(self, w) -> bool:
         return w.dtype == torch.bfloat16 and w.is_contiguous() and w.data_ptr() % 16 == 0 and w.shape[1] % 8 == 0
 
-    ACTIVATION_CODES = {"silu": 0, "gelu_tanh": 1}
+    ACTIVATION_CODES = {"silu": 0, "gelu_tanh": 1, "relu2": 2}    # relu2: the square of relu, of one product (not gated)
 
     def gated_mlp(self, h, w_gate_up, w_down, residual, inter: int, activation: str = "silu", out=None) -> None:
         """residual += down(act(gate(h)) * up(h)); ``h`` the activation rows or a DeferredNorm of them.  With
@@ -482,14 +482,16 @@ class CudaKernels:
 
     # ------------------------------------------------------- residual of several streams
     def stream_step(self, x, y=None, scale=None, mix=None, out=None, read=None, norm_weight=None, eps: float = 0.0,
-                    h=None, row_index=None, total=None) -> None:
+                    h=None, row_index=None, total=None, bias=None) -> None:
         """x float32 [T, S, W], the residual's streams.  With ``y`` (float32 [T, W]): x_t <- sum_s mix[s, t] x_s +
         out[t] * (scale * y) in place (mix [S, S], out [S], scale [W]; None = identity, ones, ones).  With ``h``
         ([rows, W], activation type): h = rmsnorm(sum_s read[s] x_s) with ``norm_weight`` and ``eps`` (read None = ones).
         With ``total`` (float32 [rows, W]): the combined row itself.  ``row_index`` (int32 [rows]) limits all of it to
         those rows of x; h and total are then indexed by the place in ``row_index``, and x itself is left as it was
-        (the new streams of those rows feed h only)."""
-        self._need_cuda(x, y, scale, mix, out, read, norm_weight, h, row_index, total)
+        (the new streams of those rows feed h only).  ``bias`` (float32 [W]): added to every stream behind the write and
+        ahead of the read."""
+        self._need_cuda(x, y, scale, mix, out, read, norm_weight, h, row_index, total, bias)
+        assert bias is None or (bias.dtype == torch.float32 and bias.numel() == x.shape[2])
         T, S, W = x.shape
         assert x.dtype == torch.float32
         for t in (y, scale, mix, out, read, norm_weight, total):
@@ -513,7 +515,7 @@ class CudaKernels:
         self._check(self.lib.tff_stream_step(_ptr(x), _c_int(S), _c_int(W), _ptr(y), _c_int(clear), _ptr(scale), _ptr(mix), _ptr(out),
                                              _ptr(read), _ptr(norm_weight), _c_float(eps), _ptr(row_index), _ptr(h),
                                              _c_int(_dt(h)) if h is not None else _c_int(0), _ptr(total), _c_int(rows),
-                                             self._stream()), "stream_step")
+                                             _ptr(bias), self._stream()), "stream_step")
         if kept_zero:
             self._acc_zero[y.data_ptr()] = bool(clear)
         self.launches += 1
@@ -550,11 +552,13 @@ class CudaKernels:
         self.launches += 1
 
     def attend_gated(self, h, w_in, freq, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, dv,
-                     scale, window, softcap, sink, v_mode, v_share, lam, gate_off, write_cache) -> None:
+                     scale, window, softcap, sink, v_mode, v_share, lam, gate_off, write_cache, pre=None) -> None:
         """The whole of a gated, capped, sink attention between its input rows and its output projection: one product
         for q, k, v and the head gates (``w_in`` rows [q | k | v | gates | padding]); rotation, value mixing, cache
         write and sigmoid of the gates; attention over the paged cache with the cap, the window, the sink and the
-        gates -> out [T, nq*dv]."""
+        gates -> out [T, nq*dv].  ``pre`` = dict(taps, conv=(q, k, v weights [channels, taps] or None), norm=(q, k weights
+        over the whole projection or None), eps, state): a short causal convolution over time on the projected q, k, v
+        and an RMS norm of all of q and of all of k, between the product and the rotation (short_conv_norm)."""
         if not write_cache:
             raise KernelError("attend_gated writes the keys and values it attends to; a borrowed cache is not supported")
         T = h.shape[0]
@@ -564,15 +568,36 @@ class CudaKernels:
         self.gemm(h, w_in, proj)
         q = torch.empty((T, nq * d), dtype=out.dtype, device=out.device)
         gates = torch.empty((T, nq), dtype=torch.float32, device=out.device) if gate_off >= 0 else None
+        if pre is not None:
+            taps = int(pre.get("taps") or 1)
+            conv = pre.get("conv") or (None, None, None)
+            norm = pre.get("norm") or (None, None)
+            widths = (nq * d, nkv * d, nkv * dv)
+            mixed = torch.empty((T, proj.shape[1]), dtype=torch.float32, device=proj.device)
+            self.short_conv_norm(proj, mixed, [(widths[0], conv[0], norm[0]), (widths[1], conv[1], norm[1]),
+                                               (widths[2], conv[2], None)], taps, float(pre.get("eps", 0.0)),
+                                 pre.get("state"), batch)
+            self.short_conv_state(proj, taps, sum(widths), pre.get("state"), batch)
+            proj = mixed
         self.qkv_finish(proj, q, None, freq, batch, block_table, kv_cache, kv_layer, page_size, nq, nkv, d, dv,
                         1.0, v_mode, v_share, lam, gate_off, gates)
         self.attention_ext(q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, dv, scale, window,
                            softcap, sink, gates)
 
+    @staticmethod
+    def _sink_args(sink, nq: int):
+        """(on, per-head scores or None) of a softmax sink given as False, True (score 0) or a float32 tensor [nq]."""
+        if isinstance(sink, torch.Tensor):
+            if sink.dtype != torch.float32 or sink.numel() != nq or not sink.is_cuda or not sink.is_contiguous():
+                raise KernelError("a sink's scores are a contiguous float32 tensor [heads] on the device")
+            return True, sink
+        return bool(sink), None
+
     def attention_ext(self, q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, dv, scale, window,
-                      softcap: float = 0.0, sink: bool = False, gates=None) -> None:
+                      softcap: float = 0.0, sink=False, gates=None) -> None:
         """q [T, nq*d] against the paged cache (slots of kv_cache.shape[-1] >= max(d, dv) elements) -> out [T, nq*dv],
-        with a cap on the scores, a sink in the softmax and a multiplier per (token, head)."""
+        with a cap on the scores, a sink in the softmax (True: of score 0; a float32 tensor [nq]: of that score per head)
+        and a multiplier per (token, head)."""
         self._need_cuda(q, block_table, out, gates)
         T = q.shape[0]
         dc = kv_cache.shape[-1]
@@ -583,15 +608,16 @@ class CudaKernels:
         if q.dtype == torch.bfloat16 and d == dv == dc and d in (64, 128) and hasattr(batch, "h_sorted_q_lens"):
             # the kernels of plain attention take the cap, the sink and the gates as well
             self.attention_bf16(q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, scale, window,
-                                extra=(float(softcap), bool(sink), gates))
+                                extra=(float(softcap), sink, gates))
             return
         c_ptr, _, c_layers, c_layer = self._cache_args(kv_cache, kv_layer)
+        sink_on, sink_val = self._sink_args(sink, nq)
         self._check(self.lib.tff_attention_generic_ext(
             _ptr(q), _c_int(_dt(q)), _c_int(q.shape[1]),
             _ptr(batch.positions), _ptr(batch.tok_req), _ptr(block_table), _c_int(block_table.shape[1]),
             c_ptr, _c_int(c_layers), _c_int(c_layer), _c_int(page_size),
             _ptr(out), _c_int(T), _c_int(nq), _c_int(nkv), _c_int(d), _c_int(dv), _c_int(dc), _c_float(scale),
-            _c_int(window), _c_float(softcap), _c_int(1 if sink else 0), _ptr(gates), self._stream()),
+            _c_int(window), _c_float(softcap), _c_int(1 if sink_on else 0), _ptr(sink_val), _ptr(gates), self._stream()),
             "attention_generic_ext")
         self.launches += 1
 
@@ -729,7 +755,10 @@ class CudaKernels:
         max_tiles, tile_rows = 0, 0
         if tiles is not None:
             tg, tr0, tre, nt, max_tiles, tile_rows = tiles
-        act = _c_int(self.ACTIVATION_CODES[activation])
+        code = self.ACTIVATION_CODES[activation]
+        if not gated and code < 2:
+            code = 0                      # a plain product: only a function of one product ("relu2") is applied to it
+        act = _c_int(code)
         ll = ctypes.c_longlong
         if self.grouped_on_tensor_cores(a, b, K, lda, a_gs, ldb, b_gs, gated, N) and tile_rows in (0, self.grouped_tile_rows(True)):
             status = self.lib.tff_gemm_grouped_mma(
@@ -777,49 +806,141 @@ class CudaKernels:
             return w.contiguous(), "interleaved"
         return torch.cat([g, u], dim=1).contiguous(), "blocked"
 
+    # ------------------------------------------------------- short convolutions, hashed pair embedding, plain activations
+    def short_conv_norm(self, proj, out, segments, taps: int, eps: float, state, batch) -> None:
+        """A causal convolution of ``taps`` taps over time on column segments of the float32 rows ``proj`` [T, ld] and the
+        RMS norm of whole segments behind it -> ``out`` [T, ld] float32 (columns beyond the segments are copied).
+        ``segments``: up to three (width, conv weights float32 [width, taps] or None, norm weight float32 [width] or
+        None), lying one behind the other from column 0.  ``state`` [slots, taps-1, C] float32 holds every request's
+        last taps-1 rows of the segments from earlier steps (csrc/short_conv.cu); short_conv_state updates it."""
+        self._need_cuda(proj, out, state)
+        T, ld = proj.shape
+        n = len(segments)
+        assert proj.dtype == out.dtype == torch.float32 and tuple(out.shape) == (T, ld) and 1 <= n <= 3
+        C = sum(int(w) for w, _, _ in segments)
+        for width, cw, nw in segments:
+            self._need_cuda(cw, nw)
+            assert cw is None or (cw.dtype == torch.float32 and tuple(cw.shape) == (width, taps))
+            assert nw is None or (nw.dtype == torch.float32 and nw.numel() == width)
+        if taps > 1:
+            assert state is not None and state.dtype == torch.float32 and tuple(state.shape[1:]) == (taps - 1, C)
+        widths = (_c_int * n)(*[int(w) for w, _, _ in segments])
+        convs = (_vp * n)(*[cw.data_ptr() if cw is not None else None for _, cw, _ in segments])
+        norms = (_vp * n)(*[nw.data_ptr() if nw is not None else None for _, _, nw in segments])
+        self._check(self.lib.tff_short_conv_norm(_ptr(proj), _c_int(ld), _ptr(out), _c_int(n), widths, convs, norms,
+                                                 _c_int(taps), _c_float(eps), _ptr(state), _ptr(batch.positions),
+                                                 _ptr(batch.tok_req), _ptr(batch.q_start), _ptr(batch.slots), _c_int(T),
+                                                 self._stream()), "short_conv_norm")
+        self.launches += 1
+
+    def short_conv_state(self, proj, taps: int, channels: int, state, batch) -> None:
+        """Behind short_conv_norm: every request's last taps-1 rows of the first ``channels`` columns of ``proj`` go to its
+        slot of ``state`` (older rows move up when the portion is shorter).  When ``proj`` is one of the accumulator
+        buffers that are kept at zero between uses, its rows are set back to zero."""
+        self._need_cuda(proj, state)
+        clear = 1 if proj.data_ptr() in self._acc_zero else 0
+        if taps <= 1 and not clear:
+            return
+        self._check(self.lib.tff_short_conv_state(_ptr(proj), _c_int(proj.shape[1]), _c_int(clear), _c_int(taps),
+                                                  _c_int(channels), _ptr(state), _ptr(batch.q_start), _ptr(batch.pos_start),
+                                                  _ptr(batch.slots), _c_int(batch.num_requests), self._stream()),
+                    "short_conv_state")
+        if clear:
+            self._acc_zero[proj.data_ptr()] = True
+        self.launches += 1
+
+    def pair_embed(self, batch, state, table, buckets: int, mul_prev: int, mul_cur: int, x, copies: int = 0) -> None:
+        """x[t] += table[(prev * mul_prev + token * mul_cur) mod buckets], prev the token before t in its request; row
+        ``buckets`` for a request's first token.  ``state`` int32 [slots, 1] holds every request's last token of earlier
+        steps and is updated.  x float32 [T, W], or [T, copies, W] with every copy getting the row."""
+        self._need_cuda(state, table, x)
+        W = x.shape[-1]
+        assert state.dtype == torch.int32 and x.dtype == torch.float32 and tuple(table.shape) == (buckets + 1, W)
+        assert x.shape[0] == batch.num_tokens and (copies == 0 or x.shape[1] == copies)
+        ll = ctypes.c_longlong
+        self._check(self.lib.tff_pair_embed(_ptr(batch.token_ids), _ptr(batch.positions), _ptr(batch.tok_req),
+                                            _ptr(batch.q_start), _ptr(batch.slots), _ptr(state), _ptr(table),
+                                            _c_int(_dt(table)), _c_int(buckets), ll(mul_prev), ll(mul_cur), _ptr(x),
+                                            _c_int(max(copies, 1)), _c_int(W), _c_int(batch.num_tokens),
+                                            _c_int(batch.num_requests), self._stream()), "pair_embed")
+        self.launches += 2
+
+    def unary_act(self, x, out, activation: str) -> None:
+        """out = act(x) element by element (may be in place); act "relu2": the square of relu."""
+        self._need_cuda(x, out)
+        assert x.dtype == out.dtype and x.numel() == out.numel()
+        self._check(self.lib.tff_unary_act(_ptr(x), _ptr(out), _c_int(_dt(x)), ctypes.c_longlong(x.numel()),
+                                           _c_int(self.ACTIVATION_CODES[activation]), self._stream()), "unary_act")
+        self.launches += 1
+
+    def plain_mlp(self, h, w_up, w_down, residual, activation: str = "relu2", out=None) -> None:
+        """residual += down(act(up(h))), a feed-forward without a gate; with ``residual`` None the result goes to ``out``."""
+        if isinstance(h, DeferredNorm):
+            h = h.materialize()
+        act = torch.empty((h.shape[0], w_up.shape[0]), dtype=h.dtype, device=h.device)
+        self.gemm(h, w_up, act)
+        self.unary_act(act, act, activation)
+        if residual is None:
+            self.gemm(act, w_down, out)
+        else:
+            self.gemm(act, w_down, residual, residual=residual)
+
     # ------------------------------------------------------- routed feed-forward (mixture of experts)
     def routed_mlp(self, h, w_router, w_gate_up, layout: str, w_down, residual, top: int, renormalize: bool = False,
-                   weight_on: str = "output", activation: str = "silu", out=None) -> None:
+                   weight_on: str = "output", activation: str = "silu", out=None, router=None) -> None:
         """residual += sum over a token's ``top`` experts of down_e(act(gate_e(x)) * up_e(x)), the experts chosen by
         the largest sigmoid(W_r h) (computed in float32), weights the scores themselves or renormalised to sum 1;
         ``weight_on`` "input": x = w h and the outputs are summed as they are; "output": x = h and the outputs are
         summed with the weights.  (w_gate_up, layout) = stack_gate_up(...) [E, 2*ff, W], w_down [E, W, ff].  With
-        ``residual`` None the sum goes to ``out``.  Six launches, no host synchronisation: route, plan, gather, two
+        ``layout`` "plain" the experts are not gated: w_gate_up is [E, ff, W] and an expert is down_e(act(up_e(x))) with
+        ``activation`` a function of one product ("relu2").  ``router`` (see moe_dispatch): softmax scores, a correction of
+        the choice, groups of experts, identity experts (router outputs beyond the E experts: weight times the input).
+        With ``residual`` None the sum goes to ``out``.  Six launches, no host synchronisation: route, plan, gather, two
         grouped products over the tokens sorted by expert, combine (a token's experts are added in the order of their
         rank)."""
         if isinstance(h, DeferredNorm):
             h = h.materialize()
         self._need_cuda(h, w_router, w_gate_up, w_down, residual, out)
         T, W = h.shape
-        E, ff = w_gate_up.shape[0], w_gate_up.shape[1] // 2
-        assert tuple(w_router.shape) == (E, W) and tuple(w_gate_up.shape) == (E, 2 * ff, W) and tuple(w_down.shape) == (E, W, ff)
-        assert weight_on in ("input", "output") and 0 < top <= E
+        plain = layout == "plain"
+        E, ff = w_gate_up.shape[0], (w_gate_up.shape[1] if plain else w_gate_up.shape[1] // 2)
+        up_rows = ff if plain else 2 * ff
+        identity = int((router or {}).get("identity", 0))
+        assert tuple(w_router.shape) == (E + identity, W) and tuple(w_gate_up.shape) == (E, up_rows, W)
+        assert tuple(w_down.shape) == (E, W, ff)
+        assert weight_on in ("input", "output") and 0 < top <= E + identity
+        if plain and activation not in ("relu2",):
+            raise KernelError(f"experts that are not gated take the activation 'relu2', got '{activation}'")
+        if not plain and activation not in ("silu", "gelu_tanh"):
+            raise KernelError(f"gated experts take the activations 'silu' and 'gelu_tanh', got '{activation}'")
         target = residual if residual is not None else out
         assert target.dtype == torch.float32 and tuple(target.shape) == (T, W)
         P = T * top
         # both products run on the same kernel (one tile table): the tensor-core one if both can
-        tc = (self.grouped_on_tensor_cores(h, w_gate_up, W, W, 0, W, 2 * ff * W, layout, ff)
+        tc = (self.grouped_on_tensor_cores(h, w_gate_up, W, W, 0, W, up_rows * W, "" if plain else layout, ff)
               and self.grouped_on_tensor_cores(h, w_down, ff, ff, 0, ff, W * ff, "", W))
-        if tc and self.GROUPED_TCGEN05 and P >= self.GROUPED_TCGEN05_FROM and W % 4 == 0:
+        if tc and self.GROUPED_TCGEN05 and P >= self.GROUPED_TCGEN05_FROM and W % 4 == 0 and ff % 8 == 0:
             # Prompt-sized: the tcgen05 product in its grouped form.  Every expert's rows are padded to whole tiles of 128
             # in the sorted order, both products write in that order, and the sum gathers a token's rows from it.
             rows = -(-(P + E * 127) // 128) * 128
-            pair_weight, row_map, tiles, x, lane_group, place = self.moe_dispatch(
-                h, w_router, top, renormalize, weight_on == "input", 128, padded_rows=rows)
+            pair_weight, row_map, tiles, x, lane_group, place, *pe = self.moe_dispatch(
+                h, w_router, top, renormalize, weight_on == "input", 128, padded_rows=rows, router=router)
             act = torch.empty((rows, ff), dtype=h.dtype, device=h.device)
-            self.gemm_tc_grouped(x, w_gate_up, act, E, 2 * ff, W, lane_group, gated=True, activation=activation)
+            self.gemm_tc_grouped(x, w_gate_up, act, E, up_rows, W, lane_group, gated=not plain, activation=activation)
             y = torch.empty((rows, W), dtype=torch.float32, device=h.device)
             self.gemm_tc_grouped(act, w_down, y, E, W, ff, lane_group)
-            self.moe_combine(y, pair_weight if weight_on == "output" else None, top, residual, target, place)
+            self.moe_combine(y, pair_weight if weight_on == "output" else None, top, residual, target, place,
+                             identity=(pe[0], pair_weight, h) if pe else None)
             return
-        pair_weight, row_map, tiles, x = self.moe_dispatch(h, w_router, top, renormalize, weight_on == "input",
-                                                           self.grouped_tile_rows(tc))
+        pair_weight, row_map, tiles, x, *pe = self.moe_dispatch(h, w_router, top, renormalize, weight_on == "input",
+                                                                self.grouped_tile_rows(tc), router=router)
         act = torch.empty((P, ff), dtype=h.dtype, device=h.device)
-        self.gemm_grouped(x, w_gate_up, act, E, 0, ff, W, W, 0, W, 2 * ff * W, ff, 0, gated=layout, activation=activation,
-                          tiles=tiles)
+        self.gemm_grouped(x, w_gate_up, act, E, 0, ff, W, W, 0, W, up_rows * W, ff, 0, gated="" if plain else layout,
+                          activation=activation, tiles=tiles)
         y = torch.empty((P, W), dtype=torch.float32, device=h.device)
         self.gemm_grouped(act, w_down, y, E, 0, W, ff, ff, 0, ff, W * ff, W, 0, tiles=tiles, row_map=row_map)
-        self.moe_combine(y, pair_weight if weight_on == "output" else None, top, residual, target)
+        self.moe_combine(y, pair_weight if weight_on == "output" else None, top, residual, target,
+                         identity=(pe[0], pair_weight, h) if pe else None)
 
     GROUPED_TCGEN05 = os.environ.get("TFFINFER_GROUPED_TCGEN05", "1") != "0"
     GROUPED_TCGEN05_FROM = 1024      # (token, expert) pairs of a step from which the experts run on the tcgen05 product
@@ -835,22 +956,33 @@ class CudaKernels:
         assert tuple(w.shape) == (groups, group_rows, K) and out.shape[0] == rows
         assert out.shape[1] == (group_rows // 2 if gated else group_rows)
         bn = 256 if (group_rows % 256 == 0 and rows >= 2048) else 128
+        unary = (not gated) and activation == "relu2"
         self._check(self.lib.tff_gemm_tc_grouped(_ptr(a), _ptr(w), _ptr(out), _c_int(_dt(out)), _c_int(rows), _c_int(groups),
                                                  _c_int(group_rows), _c_int(K), _c_int(bn), _c_int(1 if gated else 0),
-                                                 _c_int(self.ACTIVATION_CODES[activation]), _ptr(lane_group),
+                                                 _c_int(self.ACTIVATION_CODES[activation] if gated else 0), _ptr(lane_group),
                                                  self._stream()), "gemm_tc_grouped")
         self.launches += 1
+        if unary:
+            self.unary_act(out, out, "relu2")
 
     def moe_dispatch(self, h, w_router, top: int, renormalize: bool, scale_rows: bool, tile_rows: int = 0,
-                     padded_rows: int = 0):
+                     padded_rows: int = 0, router=None):
         """Router, choice and sorting of a routed feed-forward (csrc/moe.cu: route, plan, gather).  Returns
         (pair_weight float32 [T*top], row_map int32 [T*top]: sorted place -> pair, the tile table of the grouped
         products, x [T*top, W]: the tokens' rows sorted by expert, times their weight when ``scale_rows``).  With
         ``padded_rows`` (a multiple of ``tile_rows``, at least T*top + E*(tile_rows-1)) every expert's rows start at a
         multiple of ``tile_rows``, x has that many rows, and two more are returned: lane_group (int32, the expert of
-        every tile of x, -1 for tiles nobody uses) and place_of_pair (int32 [T*top])."""
+        every tile of x, -1 for tiles nobody uses) and place_of_pair (int32 [T*top]).  ``router`` = dict(score="sigmoid" |
+        "softmax", correction=float32 [outputs] or None, groups=(count, keep), identity=n): the router's last n outputs are
+        identity experts, whose pairs get no row (pair_expert -1; returned as a last, further value when n > 0)."""
         T, W = h.shape
-        E = w_router.shape[0]
+        r = router or {}
+        identity = int(r.get("identity", 0))
+        E = w_router.shape[0] - identity                          # experts that have rows
+        groups, keep = r.get("groups") or (1, 1)
+        correction = r.get("correction")
+        self._need_cuda(correction)
+        assert correction is None or (correction.dtype == torch.float32 and correction.numel() == E + identity)
         dev, P = h.device, T * top
         counts = self._moe_counts.get((E, str(dev)))
         if counts is None:
@@ -869,7 +1001,9 @@ class CudaKernels:
         place = ints[o + 3 * max_tiles + 1 + lane_tiles:] if padded_rows else None
         pair_weight = torch.empty(P, dtype=torch.float32, device=dev)
         self._check(self.lib.tff_moe_route(_ptr(h), _c_int(_dt(h)), _ptr(w_router), _c_int(_dt(w_router)), _c_int(T), _c_int(W),
-                                           _c_int(E), _c_int(top), _c_int(1 if renormalize else 0), _ptr(pair_expert),
+                                           _c_int(E + identity), _c_int(top), _c_int(1 if renormalize else 0),
+                                           _c_int(1 if r.get("score", "sigmoid") == "softmax" else 0), _ptr(correction),
+                                           _c_int(int(groups)), _c_int(int(keep)), _c_int(E), _ptr(pair_expert),
                                            _ptr(pair_weight), _ptr(counts), self._stream()), "moe_route")
         self._check(self.lib.tff_moe_plan(_ptr(counts), _c_int(E), _c_int(bm), _ptr(cursor), _ptr(tile_group), _ptr(tile_row0),
                                           _ptr(tile_row_end), _ptr(num_tiles), _c_int(bm if padded_rows else 0),
@@ -880,17 +1014,25 @@ class CudaKernels:
                                             _ptr(row_map), _ptr(place), _ptr(x), self._stream()), "moe_gather")
         self.launches += 3
         tiles = (tile_group, tile_row0, tile_row_end, num_tiles, max_tiles, bm)
+        extra = (pair_expert,) if identity else ()
         if padded_rows:
-            return pair_weight, row_map, tiles, x, lane_group, place
-        return pair_weight, row_map, tiles, x
+            return (pair_weight, row_map, tiles, x, lane_group, place) + extra
+        return (pair_weight, row_map, tiles, x) + extra
 
-    def moe_combine(self, y, pair_weight, top: int, residual, out, place_of_pair=None) -> None:
+    def moe_combine(self, y, pair_weight, top: int, residual, out, place_of_pair=None, identity=None) -> None:
         """out[t] = residual[t] + sum_k w[t, k] * y[t*top + k] in the order of k (pair_weight None: plain sum); with
-        ``place_of_pair`` the row of pair t*top + k is y[place_of_pair[t*top + k]] (y in the sorted order)."""
+        ``place_of_pair`` the row of pair t*top + k is y[place_of_pair[t*top + k]] (y in the sorted order).  ``identity`` =
+        (pair_expert, pair_weight, h): pairs whose expert is -1 add their weight times the token's row of ``h`` instead."""
         T, W = out.shape
-        self._check(self.lib.tff_moe_combine(_ptr(y), _c_int(T), _c_int(W), _c_int(top), _ptr(pair_weight),
-                                             _c_int(1 if pair_weight is not None else 0), _ptr(place_of_pair),
-                                             _ptr(residual), _ptr(out), self._stream()), "moe_combine")
+        pe, iw, h = identity if identity is not None else (None, None, None)
+        if identity is not None and pair_weight is None:
+            weights, on_output = iw, 0            # the weights are read for the identity pairs only
+        else:
+            weights, on_output = pair_weight, 1 if pair_weight is not None else 0
+        self._check(self.lib.tff_moe_combine(_ptr(y), _c_int(T), _c_int(W), _c_int(top), _ptr(weights),
+                                             _c_int(on_output), _ptr(place_of_pair),
+                                             _ptr(residual), _ptr(out), _ptr(pe), _ptr(h),
+                                             _c_int(_dt(h)) if h is not None else _c_int(0), self._stream()), "moe_combine")
         self.launches += 1
 
     # ------------------------------------------------------- gated recurrence over a state of one vector
@@ -1272,6 +1414,7 @@ class CudaKernels:
             else:
                 ws = torch.empty(need, dtype=torch.float32, device=q.device)
         softcap, sink, gates = extra
+        sink_on, sink_val = self._sink_args(sink, nq)
         self._check(self.lib.tff_attention_bf16_paged_ext(
             _ptr(q), _ptr(batch.q_start), _ptr(batch.pos_start), _ptr(req_ids), _ptr(block_table),
             _c_int(block_table.shape[1]),
@@ -1279,7 +1422,7 @@ class CudaKernels:
             _c_int(page_size),
             _ptr(out), _ptr(ws), _c_int(T), _c_int(num_requests), _c_int(max_q_len), _c_int(splits),
             _c_int(nq), _c_int(nkv), _c_int(d), _c_float(scale), _c_int(window), _c_float(softcap),
-            _c_int(1 if sink else 0), _ptr(gates), self._stream()), "attention_bf16")
+            _c_int(1 if sink_on else 0), _ptr(sink_val), _ptr(gates), self._stream()), "attention_bf16")
         self.launches += 2 if splits > 1 else 1
 
     def attention_generic(self, q, batch, block_table, kv_cache, kv_layer, page_size, out,

@@ -1,6 +1,6 @@
 """Parts a layer is made of.  Importing this package registers the built-in parts."""
-from . import norm, position, attention, mlp, block, retention, streams, latent, moe, recurrent, parallel  # noqa: F401  (registration)
-from .base import (Part, Norm, PositionEncoding, Mixer, SplitMixer, FeedForward, Block, Connector, LayerContext,
+from . import norm, position, attention, mlp, block, retention, streams, latent, moe, recurrent, parallel, embedding  # noqa: F401  (registration)
+from .base import (Part, Norm, PositionEncoding, Mixer, SplitMixer, FeedForward, Block, Connector, EmbeddingExtra, LayerContext,
                    WeightSpec, KVNeed, StateNeed, MATRIX, VECTOR, INT_TABLE)
 from .description import PartSpec, LayerSpec, ScheduleEntry, ModelDescription
 from .model import Model, CacheBinding, build_part

@@ -19,7 +19,7 @@ from typing import Dict, Optional
 import torch
 
 from ..registry import register_part
-from .base import Mixer, SplitMixer, WeightSpec, MATRIX, VECTOR, KVNeed, LayerContext
+from .base import Mixer, SplitMixer, WeightSpec, MATRIX, VECTOR, KVNeed, StateNeed, LayerContext
 
 
 @register_part("mixer", "gqa_attention")
@@ -92,7 +92,13 @@ class GatedSinkAttention(Mixer):
     * a rotation of part of the head given by the layer's position encoding (``frequencies()``);
     * scores ``(q . k) * softmax_scale``, then ``softcap * tanh(score / softcap)`` when ``softcap`` > 0;
     * a sliding ``window`` (a query at position p sees keys p-window+1 .. p; 0 = all earlier keys);
-    * ``sink``: one more term in the softmax's denominator, a key of score 0 without a value;
+    * ``sink``: one more term in the softmax's denominator, a key without a value: True, of score 0; "learned", of a
+      learned score per head (tensor "sink" [heads]), which is neither scaled nor capped;
+    * ``conv_taps`` > 0: a short causal convolution over time on every channel of the projected q, k and v (tensors
+      "q_conv", "k_conv", "v_conv" [channels, taps]; y_t = sum_j w[:, j] u_(t - taps + 1 + j), zeros before the
+      sequence's start), directly behind the projection; a request's last taps-1 projected rows are kept in a state slot;
+    * ``qk_norm`` "whole": an RMS norm over ALL of a token's q (and of its k) at once, with plain weights "q_norm"
+      [heads * head_dim] and "k_norm" and ``qk_norm_eps``, behind the convolution and ahead of the rotation;
     * ``value_mix``: "source" leaves this layer's values of the step's tokens in ``ctx.shared[value_key]``;
       "mix" replaces its own by ``(1 - lambda) v + lambda v_source`` with a learned scalar lambda before they are
       cached; "none" does neither;
@@ -105,13 +111,25 @@ class GatedSinkAttention(Mixer):
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, v_head_dim: int = 0,
                  softmax_scale: Optional[float] = None, softcap: float = 0.0, window: int = 0, sink: bool = False,
                  value_mix: str = "none", value_key: str = "values", head_gate: bool = False,
-                 lambda_tensor: bool = False, names: Optional[Dict[str, str]] = None, prefix: str = ""):
+                 lambda_tensor: bool = False, conv_taps: int = 0, qk_norm: str = "none", qk_norm_eps: float = 0.0,
+                 names: Optional[Dict[str, str]] = None, prefix: str = ""):
         super().__init__(prefix)
         self.hidden_size, self.num_heads, self.num_kv_heads = int(hidden_size), int(num_heads), int(num_kv_heads)
         self.head_dim = int(head_dim)
         self.v_head_dim = int(v_head_dim) if v_head_dim else int(head_dim)
         self.scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(self.head_dim)
-        self.softcap, self.window, self.sink = float(softcap), int(window), bool(sink)
+        self.softcap, self.window = float(softcap), int(window)
+        if sink not in (False, True, "learned"):
+            raise ValueError(f"sink must be False, True or 'learned', got {sink!r}")
+        self.sink = sink
+        self.conv_taps = int(conv_taps)
+        if self.conv_taps < 0 or self.conv_taps > 8:
+            raise ValueError(f"conv_taps must lie in 0 .. 8, got {self.conv_taps}")
+        if qk_norm not in ("none", "whole"):
+            raise ValueError(f"qk_norm must be 'none' or 'whole', got '{qk_norm}'")
+        if qk_norm == "whole" and not qk_norm_eps > 0:
+            raise ValueError("qk_norm needs qk_norm_eps > 0")
+        self.qk_norm, self.qk_norm_eps = qk_norm, float(qk_norm_eps)
         if value_mix not in ("none", "source", "mix"):
             raise ValueError(f"value_mix must be 'none', 'source' or 'mix', got '{value_mix}'")
         self.value_mix, self.value_key, self.head_gate = value_mix, value_key, bool(head_gate)
@@ -119,16 +137,21 @@ class GatedSinkAttention(Mixer):
         if self.num_heads % self.num_kv_heads:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
         self.names = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
-                      "gate": "gate_proj.weight", "lambda": "value_lambda"}
+                      "gate": "gate_proj.weight", "lambda": "value_lambda", "sink": "sink", "q_conv": "q_conv",
+                      "k_conv": "k_conv", "v_conv": "v_conv", "q_norm": "q_norm", "k_norm": "k_norm"}
         self.names.update(names or {})
         self.q_width = self.num_heads * self.head_dim
         self.k_width = self.num_kv_heads * self.head_dim
         self.v_width = self.num_kv_heads * self.v_head_dim
         self.cache_dim = max(self.head_dim, self.v_head_dim)     # a cache slot holds a key or a value
-        self.w_in = self.w_o = self.lam = None
+        self.w_in = self.w_o = self.lam = self.sink_w = None
+        self.conv_w = self.norm_w = None
 
     def cache_need(self):
-        return KVNeed(self.num_kv_heads, self.cache_dim, self.window)
+        kv = KVNeed(self.num_kv_heads, self.cache_dim, self.window)
+        if self.conv_taps > 1:        # the projected rows the convolution still needs when the next step comes
+            return kv, StateNeed((self.conv_taps - 1, self.q_width + self.k_width + self.v_width), "float32")
+        return kv
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         n = self.names
@@ -140,6 +163,14 @@ class GatedSinkAttention(Mixer):
             s[n["gate"]] = WeightSpec((self.num_heads, self.hidden_size), MATRIX)
         # a layer that mixes nothing may still carry the scalar in a file: it is accepted and not used
         s[n["lambda"]] = WeightSpec((), VECTOR, init="normal", init_scale=0.3, optional=not self.lambda_tensor)
+        if self.sink == "learned":
+            s[n["sink"]] = WeightSpec((self.num_heads,), VECTOR, init="normal", init_scale=1.0)
+        if self.conv_taps > 0:
+            for which, width in (("q_conv", self.q_width), ("k_conv", self.k_width), ("v_conv", self.v_width)):
+                s[n[which]] = WeightSpec((width, self.conv_taps), VECTOR, init="normal", init_scale=0.5)
+        if self.qk_norm == "whole":
+            s[n["q_norm"]] = WeightSpec((self.q_width,), VECTOR, init="one_plus_normal")
+            s[n["k_norm"]] = WeightSpec((self.k_width,), VECTOR, init="one_plus_normal")
         return s
 
     def load(self, tensors, ops, act_dtype) -> None:
@@ -157,6 +188,12 @@ class GatedSinkAttention(Mixer):
         self.w_o = tensors[n["o"]]
         if self.lambda_tensor:
             self.lam = tensors[n["lambda"]].reshape(1).contiguous()
+        if self.sink == "learned":
+            self.sink_w = tensors[n["sink"]].to(torch.float32).contiguous()
+        if self.conv_taps > 0:
+            self.conv_w = tuple(tensors[n[w]].to(torch.float32).contiguous() for w in ("q_conv", "k_conv", "v_conv"))
+        if self.qk_norm == "whole":
+            self.norm_w = (tensors[n["q_norm"]].to(torch.float32).contiguous(), tensors[n["k_norm"]].to(torch.float32).contiguous())
 
     def forward(self, h, ctx: LayerContext, residual):
         ops, batch = ctx.ops, ctx.batch
@@ -172,11 +209,16 @@ class GatedSinkAttention(Mixer):
                 raise ValueError(f"value_mix='mix' needs the values of an earlier layer of this step under "
                                  f"'{self.value_key}' with {self.v_width} elements a token")
         attn = torch.empty((T, self.num_heads * self.v_head_dim), dtype=h.dtype, device=h.device)
+        pre = None
+        if self.conv_taps > 0 or self.qk_norm == "whole":
+            pre = dict(taps=max(self.conv_taps, 1), conv=self.conv_w, norm=self.norm_w, eps=self.qk_norm_eps,
+                       state=ctx.state if self.conv_taps > 1 else None)
         ops.attend_gated(h, self.w_in, freq, batch, ctx.block_table, ctx.kv_cache, ctx.kv_layer, ctx.page_size, attn,
                          self.num_heads, self.num_kv_heads, self.head_dim, self.v_head_dim, self.scale, self.window,
-                         self.softcap, self.sink, {"none": 0, "source": 1, "mix": 2}[self.value_mix], share,
+                         self.softcap, self.sink_w if self.sink == "learned" else self.sink,
+                         {"none": 0, "source": 1, "mix": 2}[self.value_mix], share,
                          self.lam if self.value_mix == "mix" else None,
-                         self.gate_off if self.head_gate else -1, ctx.write_cache)
+                         self.gate_off if self.head_gate else -1, ctx.write_cache, pre=pre)
         if residual is None:
             out = ops.sublayer_output(T, self.hidden_size, h.device, h.dtype)
             ops.gemm(attn, self.w_o, out)

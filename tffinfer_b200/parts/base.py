@@ -196,6 +196,20 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class EmbeddingExtra(Part):
+    """Something added to the token embedding's output before the first layer (registry family "embedding").
+
+    state_need() -> StateNeed | None: what it keeps per request between steps (the previous token, say)
+    forward(x, batch, ops, state, copies): adds to x, float32 [T, hidden] (copies == 0) or [T, copies, hidden] with
+    every copy getting the same; ``state`` is its [slots, ...] tensor, indexed with batch.slots on the device.
+    """
+    def state_need(self):
+        return None
+
+    def forward(self, x: torch.Tensor, batch, ops, state, copies: int = 0) -> None:
+        raise NotImplementedError
+
+
 class Connector(Part):
     """How a sublayer reads its input from the residual and how its output joins it, where that is more than
     ``norm(x)`` and ``x + y``: the residual is then a :class:`parts.streams.ResidualStreams`.

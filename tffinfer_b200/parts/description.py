@@ -45,9 +45,12 @@ class ScheduleEntry:
     """One run of a layer.  ``layer`` indexes ``ModelDescription.layers`` and may
     repeat (the same weights run twice, each run with a cache of its own).
     ``cache_of`` names an EARLIER schedule entry whose cache this run reads instead of
-    keeping one (it then writes nothing)."""
+    keeping one (it then writes nothing).  ``add_vector`` = (tensor name, row): that row of a
+    [rows, hidden] tensor of the model (``ModelDescription.vector_tables``) is added to the
+    residual right before this run."""
     layer: int
     cache_of: Optional[int] = None
+    add_vector: Optional[tuple] = None
 
 
 @dataclass
@@ -65,6 +68,10 @@ class ModelDescription:
     embed_scale: float = 1.0              # the embedding rows are multiplied by this (1: as they are)
     logit_scale: float = 1.0              # the logits are multiplied by this ...
     logit_softcap: float = 0.0            # ... and then, if > 0, squashed: softcap * tanh(logit / softcap)
+    embed_extras: List[PartSpec] = field(default_factory=list)   # parts (registry family "embedding") that add to the
+                                          # embedding's output, e.g. a table indexed by a hash of neighbouring tokens
+    vector_tables: Dict[str, int] = field(default_factory=dict)  # tensor name -> rows of a [rows, hidden] table whose
+                                          # rows schedule entries add to the residual (ScheduleEntry.add_vector)
     streams: int = 0                      # 0: the residual is one tensor [T, hidden].  S >= 1: it is S copies of the
                                           # embedding output (parts/streams.py), read and written through the layers'
                                           # connectors; the final norm reads their sum
@@ -78,6 +85,10 @@ class ModelDescription:
                     raise ValueError(f"schedule[{i}].cache_of must name an earlier entry, got {e.cache_of}")
                 if self.schedule[e.cache_of].cache_of is not None:
                     raise ValueError(f"schedule[{i}].cache_of names entry {e.cache_of}, which keeps no cache itself")
+            if e.add_vector is not None:
+                name, row = e.add_vector
+                if name not in self.vector_tables or not (0 <= row < self.vector_tables[name]):
+                    raise ValueError(f"schedule[{i}].add_vector names row {row} of '{name}', which the model does not have")
         for i, l in enumerate(self.layers):
             if l.position is not None and l.position not in self.positions:
                 raise ValueError(f"layer {i} names position encoding '{l.position}', which is not defined")

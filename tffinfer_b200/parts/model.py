@@ -13,7 +13,7 @@ from typing import Dict, List, Optional
 import torch
 
 from ..registry import get_part
-from .base import Part, Block, LayerContext, WeightSpec, MATRIX
+from .base import Part, Block, LayerContext, WeightSpec, MATRIX, VECTOR
 from .description import ModelDescription, PartSpec
 
 
@@ -49,13 +49,16 @@ class Model:
                 extra_norms={name: build_part("norm", ps) for name, ps in ls.extra_norms.items()}, **kw))
         self.layer_position = [self.positions[ls.position] if ls.position else None for ls in desc.layers]
         self.final_norm = build_part("norm", desc.final_norm)
+        self.embed_extras = [build_part("embedding", ps) for ps in desc.embed_extras]
+        self.embed_state_index: List[Optional[int]] = [None] * len(self.embed_extras)   # set by the runner
+        self.vector_tables: Dict[str, torch.Tensor] = {}
         self.embed: Optional[torch.Tensor] = None
         self.lm_head: Optional[torch.Tensor] = None
         self.layer_hook = None      # optional callable(run index, float32 [T, hidden]): the residual after every layer run
 
     # ---------------------------------------------------------------- weights
     def all_parts(self) -> List[Part]:
-        parts: List[Part] = list(self.positions.values())
+        parts: List[Part] = list(self.positions.values()) + list(self.embed_extras)
         for b in self.blocks:
             parts.extend(b.parts())
         parts.append(self.final_norm)
@@ -66,6 +69,8 @@ class Model:
         out = {d.embed_name: WeightSpec((d.vocab_size, d.hidden_size), MATRIX)}
         if d.lm_head_name is not None:
             out[d.lm_head_name] = WeightSpec((d.vocab_size, d.hidden_size), MATRIX)
+        for name, rows in d.vector_tables.items():
+            out[name] = WeightSpec((rows, d.hidden_size), VECTOR, init="normal", init_scale=0.1)
         for p in self.all_parts():
             for rel, spec in p.weight_specs().items():
                 name = p.full_name(rel)
@@ -78,6 +83,7 @@ class Model:
         d = self.desc
         self.embed = tensors[d.embed_name]
         self.lm_head = tensors[d.lm_head_name] if d.lm_head_name is not None else self.embed
+        self.vector_tables = {name: tensors[name].to(torch.float32).contiguous() for name in d.vector_tables}
         for p in self.all_parts():
             p.load({rel: tensors[p.full_name(rel)] for rel in p.weight_specs() if p.full_name(rel) in tensors}, ops, act_dtype)
         for pos in self.positions.values():
@@ -93,6 +99,10 @@ class Model:
             needs.append(None if e.cache_of is not None else need)
         return needs
 
+    def extra_state_needs(self):
+        """One entry per part of ``embed_extras``: StateNeed | None."""
+        return [p.state_need() for p in self.embed_extras]
+
     # ---------------------------------------------------------------- forward
     def forward(self, batch, ops, act_dtype, bindings: List[CacheBinding], kv_caches, block_tables,
                 page_size: int, states) -> torch.Tensor:
@@ -107,6 +117,8 @@ class Model:
         else:
             x = torch.empty((T, d.hidden_size), dtype=torch.float32, device=self.embed.device)
             ops.embed(batch.token_ids, self.embed, x, d.embed_scale)
+        for p, si in zip(self.embed_extras, self.embed_state_index):
+            p.forward(x.x if d.streams > 0 else x, batch, ops, states[si] if si is not None else None, copies=d.streams)
         for pos in self.positions.values():
             x = pos.embed(x, batch, ops)
         shared: Dict[str, torch.Tensor] = {}
@@ -120,6 +132,12 @@ class Model:
                 page_size=page_size, write_cache=b.write,
                 state=states[b.state_index] if b.state_index is not None else None,
                 position=self.layer_position[entry.layer], shared=shared)
+            if entry.add_vector is not None:
+                vec = self.vector_tables[entry.add_vector[0]][entry.add_vector[1]]
+                if d.streams > 0:
+                    x.add_vector(vec)              # runs with the layer's read of the residual
+                else:
+                    ops.stream_step(x.view(T, 1, d.hidden_size), bias=vec)
             x = self.blocks[entry.layer].forward(x, ctx, act_dtype)
             if self.layer_hook is not None:
                 self.layer_hook(e, x.total() if d.streams > 0 else x)

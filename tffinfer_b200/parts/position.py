@@ -36,16 +36,17 @@ class NoPosition(PositionEncoding):
         super().__init__(prefix)
 
 
-def scaled_frequencies(rot_dim: int, base: float, scaling=None):
+def scaled_frequencies(rot_dim: int, base: float, scaling=None, linear_factor: float = 1.0):
     """(frequencies as a list of rot_dim/2 floats, magnitude of cos and sin).  Plain: f_i = base^(-2i/rot_dim),
     magnitude 1.  With ``scaling`` = (factor, original, fast, slow), the YaRN rule: the dimension at which a
     position of ``original`` makes ``t`` turns is dim(t) = rot_dim ln(original / (2 pi t)) / (2 ln base);
     between lo = max(floor(dim(fast)), 0) and hi = min(ceil(dim(slow)), rot_dim - 1) a ramp r_i =
     clamp((i - lo) / max(hi - lo, 0.001), 0, 1) takes f_i over to f_i / factor (f_i (1 - r_i) + f_i / factor r_i),
-    and cos and sin are multiplied by 0.1 ln(factor) + 1.  Evaluated in double; the caller rounds once."""
+    and cos and sin are multiplied by 0.1 ln(factor) + 1.  ``linear_factor``: every frequency is divided by it (linear
+    scaling of the positions).  Evaluated in double; the caller rounds once."""
     import math
     half = rot_dim // 2
-    f = [base ** (-2.0 * i / rot_dim) for i in range(half)]
+    f = [base ** (-2.0 * i / rot_dim) / float(linear_factor) for i in range(half)]
     if scaling is None:
         return f, 1.0
     factor, original, fast, slow = (float(v) for v in scaling)
@@ -67,8 +68,10 @@ class ScaledRotary(PositionEncoding):
     """A rotation of the first ``rotary_dim`` dimensions of a head whose angles are computed from the position
     where they are applied (no table, so no longest position): pair i at position p turns by float32(p) *
     float32(f_i).  ``pairing``: "interleaved" pairs dimension 2i with 2i+1, "halves" pairs i with i + rotary_dim/2.
-    ``scaling`` rescales the frequencies and the magnitude (scaled_frequencies above)."""
-    def __init__(self, rotary_dim: int, theta: float, pairing: str = "halves", scaling=None, prefix: str = ""):
+    ``scaling`` rescales the frequencies and the magnitude, ``linear_factor`` divides every frequency (scaled_frequencies
+    above)."""
+    def __init__(self, rotary_dim: int, theta: float, pairing: str = "halves", scaling=None, linear_factor: float = 1.0,
+                 prefix: str = ""):
         super().__init__(prefix)
         self.rotary_dim = int(rotary_dim)
         self.theta = float(theta)
@@ -78,11 +81,14 @@ class ScaledRotary(PositionEncoding):
             raise ValueError(f"rotary_dim {self.rotary_dim} must be even and positive")
         self.interleaved = pairing == "interleaved"
         self.scaling = tuple(scaling) if scaling is not None else None
+        self.linear_factor = float(linear_factor)
+        if not self.linear_factor > 0:
+            raise ValueError("linear_factor must be positive")
         self.freq = None
         self.magnitude = 1.0
 
     def prepare(self, ops, device, max_position: int) -> None:
-        f, self.magnitude = scaled_frequencies(self.rotary_dim, self.theta, self.scaling)
+        f, self.magnitude = scaled_frequencies(self.rotary_dim, self.theta, self.scaling, self.linear_factor)
         self.freq = torch.tensor(f, dtype=torch.float64).to(torch.float32).to(device)
 
     def frequencies(self):

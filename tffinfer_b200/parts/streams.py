@@ -33,6 +33,7 @@ class ResidualStreams:
         self.ops = ops
         self.streams = x.shape[1]
         self.pending = None            # (y, scale, mix, out) of the write that is still to come
+        self.pending_bias = None       # a vector [hidden] that is still to be added to every stream, behind that write
 
     @classmethod
     def from_embedding(cls, token_ids, table, scale: float, streams: int, ops) -> "ResidualStreams":
@@ -45,14 +46,20 @@ class ResidualStreams:
         return self.x.device
 
     def write(self, y, scale, mix, out) -> None:
-        self.flush()
+        self.flush()                   # (a vector still to be added comes ahead of this write)
         self.pending = (y, scale, mix, out)
 
+    def add_vector(self, vec: torch.Tensor) -> None:
+        """x_s <- x_s + vec for every stream (float32 [hidden]); like a write, it runs with the next read."""
+        if self.pending_bias is not None:
+            self.flush()
+        self.pending_bias = vec
+
     def flush(self) -> None:
-        if self.pending is not None:
-            y, scale, mix, out = self.pending
-            self.pending = None
-            self.ops.stream_step(self.x, y=y, scale=scale, mix=mix, out=out)
+        if self.pending is not None or self.pending_bias is not None:
+            y, scale, mix, out = self.pending if self.pending is not None else (None, None, None, None)
+            bias, self.pending, self.pending_bias = self.pending_bias, None, None
+            self.ops.stream_step(self.x, y=y, scale=scale, mix=mix, out=out, bias=bias)
 
     def read(self, read_w, norm, ops, out_dtype, row_index=None) -> torch.Tensor:
         """norm(sum_s read_w[s] x_s) at every row, or at the rows of ``row_index``; applies the write that is
@@ -61,9 +68,9 @@ class ResidualStreams:
         rows = self.x.shape[0] if row_index is None else row_index.shape[0]
         h = torch.empty((rows, self.x.shape[2]), dtype=out_dtype, device=self.x.device)
         y, scale, mix, out = self.pending if self.pending is not None else (None, None, None, None)
-        self.pending = None
+        bias, self.pending, self.pending_bias = self.pending_bias, None, None
         ops.stream_step(self.x, y=y, scale=scale, mix=mix, out=out, read=read_w, norm_weight=norm.weight,
-                        eps=norm.eps, h=h, row_index=row_index)
+                        eps=norm.eps, h=h, row_index=row_index, bias=bias)
         return h
 
     def total(self) -> torch.Tensor:
@@ -80,12 +87,13 @@ class HyperConnection(Connector):
     (relative to the prefix) of "read" [S], "write" [S], "mix" [S, S] and "scale" [hidden]."""
 
     def __init__(self, streams: int, hidden_size: int, learned: bool = True, layer_scale: bool = True,
-                 names: Optional[Dict[str, str]] = None, prefix: str = ""):
+                 multiplier: float = 1.0, names: Optional[Dict[str, str]] = None, prefix: str = ""):
         super().__init__(prefix)
         self.streams = int(streams)
         self.hidden_size = int(hidden_size)
         self.learned = bool(learned)
         self.layer_scale = bool(layer_scale)
+        self.multiplier = float(multiplier)       # a constant that multiplies every write (with the write vector)
         self.names = {"read": "in", "write": "out", "mix": "mix", "scale": "scale"}
         self.names.update(names or {})
         self.read_w = self.write_w = self.mix_w = self.scale_w = None
@@ -104,6 +112,8 @@ class HyperConnection(Connector):
         n = self.names
         if self.learned:
             self.read_w, self.write_w, self.mix_w = tensors[n["read"]], tensors[n["write"]], tensors[n["mix"]]
+            if self.multiplier != 1.0:
+                self.write_w = (self.write_w.to(torch.float32) * self.multiplier).contiguous()
         if self.layer_scale:
             self.scale_w = tensors[n["scale"]]
 
@@ -111,6 +121,8 @@ class HyperConnection(Connector):
         return x.read(self.read_w, norm, ops, out_dtype)
 
     def write(self, x: ResidualStreams, y) -> None:
+        if self.write_w is None and self.multiplier != 1.0:       # no learned write vector: the constant alone
+            self.write_w = torch.full((self.streams,), self.multiplier, dtype=torch.float32, device=x.device)
         x.write(y, self.scale_w, self.mix_w, self.write_w)
 
 
@@ -134,4 +146,27 @@ class StreamPreNormBlock(Block):
             join = self.connectors["ffn"]
             h = join.read(x, self.ffn_norm, ctx.ops, act_dtype)
             join.write(x, self.feed_forward.forward(h, ctx, residual=None))
+        return x
+
+
+@register_part("block", "stream_parallel")
+class StreamParallelBlock(Block):
+    """The mixer and the feed-forward side by side on ONE norm's output: ``x <- write(mixer(h) + feed_forward(h))`` with
+    ``h = norm(read(x))``, through the connector ``connectors["layer"]`` (which carries any multiplier of the sum).  The
+    feed-forward adds into the mixer's output rows; a layer without a feed-forward is the mixer alone."""
+
+    def __init__(self, mixer, feed_forward=None, mixer_norm=None, ffn_norm=None, extra_norms=None, connectors=None):
+        super().__init__(mixer, feed_forward, mixer_norm, ffn_norm, extra_norms, connectors)
+        if mixer_norm is None or "layer" not in self.connectors:
+            raise ValueError("the stream_parallel arrangement needs mixer_norm and a 'layer' connector")
+        if ffn_norm is not None:
+            raise ValueError("the stream_parallel arrangement has one norm: both sublayers read its output")
+
+    def forward(self, x: ResidualStreams, ctx: LayerContext, act_dtype):
+        join = self.connectors["layer"]
+        h = join.read(x, self.mixer_norm, ctx.ops, act_dtype)
+        y = self.mixer.forward(h, ctx, residual=None)
+        if self.feed_forward is not None:
+            y = self.feed_forward.forward(h, ctx, residual=y)
+        join.write(x, y)
         return x

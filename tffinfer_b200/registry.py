@@ -9,7 +9,7 @@ Two kinds of entries exist:
   made of parts) -- cf. ``REGISTER_MODULE_OBJECT(QWen3Creator, ModelCreatorBase,
   MODEL_CREATOR_FLAG, "qwen3")`` at src/core/model/qwen3/QWen3Creator.cpp:11-12;
 * parts: (family, kind) -> class, with family one of ``mixer``, ``feed_forward``,
-  ``norm``, ``position``, ``block``, ``connector``.
+  ``norm``, ``position``, ``block``, ``connector``, ``embedding``.
 
 Registration is open: code outside the package (a test, a plug-in) may register a
 new part or a whole architecture without touching any file of the framework.
@@ -19,7 +19,7 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Any, Callable, Dict, Tuple
 
-PART_FAMILIES = ("mixer", "feed_forward", "norm", "position", "block", "connector")
+PART_FAMILIES = ("mixer", "feed_forward", "norm", "position", "block", "connector", "embedding")
 
 
 class RegistryError(KeyError):
