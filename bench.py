@@ -650,19 +650,117 @@ def run_dominex(steps: int, warmup: int, sizes=None) -> int:
     return 0
 
 
+# The Sadupel design beside Dominex (the closest of the other models: layers listed one by one, routed experts behind a
+# softmax attention over the paged cache) at the same width: (width, heads, kv heads, dim, taps, experts, identity
+# experts, chosen, groups, kept groups, expert ff, shared ff).  Six layers, of which layers 2 and 3 run twice in a row
+# (eight layer runs, as many as the twin has layers); the experts are not gated, so their ff is 1.5 times the twin's for
+# the same arithmetic a chosen expert.
+SADUPEL_SIZES = {"2k": (2048, 16, 4, 128, 4, 14, 2, 2, 4, 2, 4608, 2048),
+                 "4k": (4096, 32, 8, 128, 4, 14, 2, 2, 4, 2, 9216, 4096)}
+SADUPEL_RUNS = 8
+
+
+def sadupel_engine(size: str, max_live: int, cache_tokens: int, graphs: bool, step_tokens: int):
+    import torch
+    import tffinfer_b200 as tff
+    from tffinfer_b200.config.sadupel_config import SadupelConfig, SadupelLayer, SadupelExperts
+    from tffinfer_b200.weights import random_tensors_on_device
+    W, H, G, D, TAPS, E, IDENT, TOP, GROUPS, KEEP, F, SF = SADUPEL_SIZES[size]
+    moe = SadupelExperts(ff=F, experts=E, top=TOP, identity=IDENT, groups=GROUPS, keep=KEEP, shared_ff=SF)
+    layer = SadupelLayer(heads=H, kv_heads=G, dim=D, vdim=D, conv=TAPS, scale=D ** -0.5, softcap=30.0, rot_base=5e5,
+                         rot_dims=D // 2, rot_factor=4.0, mlp=moe)
+    cfg = SadupelConfig("Sadupel", vocab_size=TIPEZEN_VOCAB, hidden_size=W, norm_eps=1e-6, residual_mult=0.5,
+                        bigram=(65521, 31, 17), loop=(2, 4, 2), layers=(layer,) * 6)
+    assert len(cfg.runs()) == SADUPEL_RUNS
+    tensors = random_tensors_on_device(cfg, 0, "cuda", "bfloat16")
+    ecfg = tff.EngineConfig(dtype="bfloat16", page_size=PAGE_SIZE, max_cache_tokens=cache_tokens, max_live_requests=max_live,
+                            max_tokens_per_step=step_tokens, max_model_len=8192, use_cuda_graphs=graphs)
+    runner = tff.ModelRunner(config=cfg, tensors=tensors, engine_config=ecfg)
+    del tensors
+    torch.cuda.empty_cache()
+    return tff.Engine(runner=runner), cfg
+
+
+def run_sadupel(steps: int, warmup: int, sizes=None) -> int:
+    """Prefill and decode throughput of the Sadupel design beside Dominex at the same layer sizes, one JSON line a
+    point, and for each model the device time of a step by kind of kernel call; for Sadupel also what its own kernels
+    reach: the convolution-and-norm kernel, the hashed embedding, the router and the activation kernels as a fraction of
+    the measured copy rate, the attention and the experts' grouped products in TFLOP/s."""
+    import torch
+    peaks = load_peaks()
+    steps = min(steps, 32)
+    P = PROMPT_LEN
+    for size in (sizes or SADUPEL_SIZES):
+        W, H, G, D, TAPS, E, IDENT, TOP, GROUPS, KEEP, F, SF = SADUPEL_SIZES[size]
+        for model, make in (("sadupel", sadupel_engine), ("dominex", dominex_engine)):
+            need = 64 * (P + warmup + steps + 64 + 72)
+            engine, cfg = make(size, 64, need, True, P)
+            pms = prefill_run(engine, iters=3, warmup=2, seed=1, prompt_len=P)
+            print(json.dumps({"point": "prefill", "model": model, "size": size, "layers": TIPEZEN_LAYERS, "tokens": P,
+                              "ms": round(pms, 3), "tok_s": round(P / (pms / 1e3), 1)}), flush=True)
+            for b in (8, 64):
+                run = decode_run(engine, b, steps, warmup, seed=b, prompt_len=P)
+                print(json.dumps({"point": "decode", "model": model, "size": size, "layers": TIPEZEN_LAYERS, "batch": b,
+                                  "context": round(run["mean_context"]), "tok_s": round(run["tok_s"], 1),
+                                  "ms_per_step": round(run["ms_per_step"], 4), "launches_per_step": run["launches"] // steps}),
+                      flush=True)
+            del engine
+            torch.cuda.empty_cache()
+            engine, cfg = make(size, 8, 8 * (P + 64), False, P)
+            kinds = traced_kinds(engine, P, 8)
+            line = {"point": "kernels", "model": model, "size": size, "prefill_tokens": P, "decode_batch": 8,
+                    "prefill_ms_by_kind": kinds.get("prefill"), "decode_ms_by_kind": kinds.get("decode"), "peaks": peaks["source"]}
+            if model == "sadupel":
+                nl = SADUPEL_RUNS
+                C = (H + 2 * G) * D                       # channels of q, k and v together
+                ld = -(-(C + H) // 8) * 8                 # with the head gates, padded
+                # convolution and norm: a row of float32 accumulators read and a float32 row written (the taps' older rows
+                # come from the cache of the chip); the state kernel reads the last rows again and clears nothing here
+                conv_b = lambda T: nl * T * ld * 4 * 2
+                finish_b = lambda T: nl * T * (ld * 4 + H * D * 2 + 2 * G * D * 2 + H * 4)
+                # the share of chosen outputs that are experts with rows is not known ahead: all TOP are counted
+                expert_flops = nl * P * TOP * 2 * 2.0 * W * F
+                attn_flops = nl * H * (P * (P + 1) / 2.0) * 2.0 * (2 * D)
+                fr = {}
+                for step, T in (("prefill", P), ("decode", 8)):
+                    k = kinds.get(step) or {}
+                    if "short_conv_norm" in k:
+                        fr[f"{step}_short_conv_norm_hbm_frac"] = round(conv_b(T) / (k["short_conv_norm"][1] / 1e3) / 1e9 / peaks["hbm_gbs"], 4)
+                    if "qkv_finish" in k:
+                        fr[f"{step}_qkv_finish_hbm_frac"] = round(finish_b(T) / (k["qkv_finish"][1] / 1e3) / 1e9 / peaks["hbm_gbs"], 4)
+                k = kinds.get("prefill") or {}
+                if "gemm_tc_grouped" in k:
+                    fr["prefill_experts_tcgen05_tflops"] = round(expert_flops / (k["gemm_tc_grouped"][1] / 1e3) / 1e12, 2)
+                    fr["prefill_experts_tcgen05_frac"] = round(fr["prefill_experts_tcgen05_tflops"] / peaks["bf16_tflops"], 4)
+                if "attention_bf16" in k:
+                    fr["prefill_attention_tflops"] = round(attn_flops / (k["attention_bf16"][1] / 1e3) / 1e12, 2)
+                kd = kinds.get("decode") or {}
+                if "gemm_grouped" in kd:
+                    w_b = nl * min(E, 8 * TOP) * 2 * W * F * 2
+                    fr["decode_gemm_grouped_hbm_frac"] = round(w_b / (kd["gemm_grouped"][1] / 1e3) / 1e9 / peaks["hbm_gbs"], 4)
+                if "attention_bf16" in kd:
+                    cache_b = nl * 8 * P * 2 * G * D * 2
+                    fr["decode_attention_hbm_frac"] = round(cache_b / (kd["attention_bf16"][1] / 1e3) / 1e9 / peaks["hbm_gbs"], 4)
+                line["fractions"] = fr
+            print(json.dumps(line), flush=True)
+            del engine
+            torch.cuda.empty_cache()
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="headline", choices=["headline", "sweep", "attn_decode", "shapes", "tipezen", "dominex"] + sorted(WORKLOADS),
+    ap.add_argument("--workload", default="headline", choices=["headline", "sweep", "attn_decode", "shapes", "tipezen", "dominex", "sadupel"] + sorted(WORKLOADS),
                     help="headline: the decode/prefill benchmark; sweep: the same shape at further batch sizes and "
                          "context lengths; attn_decode: the decode attention alone; shapes: the layer sizes of the other "
-                         "models of the family; tipezen: the Tipezen design beside Qwen3 at equal layer sizes; dominex: the Dominex design beside Tipezen at equal layer sizes; else a whole workload through "
+                         "models of the family; tipezen: the Tipezen design beside Qwen3 at equal layer sizes; dominex: the Dominex design beside Tipezen at equal layer sizes; sadupel: the Sadupel design beside Dominex at equal layer sizes; else a whole workload through "
                          "the scheduler")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--size", default="", help="with --workload dominex: one of its layer sizes (2k, 4k) instead of all")
+    ap.add_argument("--size", default="", help="with --workload dominex or sadupel: one of its layer sizes (2k, 4k) instead of all")
     ap.add_argument("--layers", type=int, default=SHAPE["num_layers"],
                     help="fewer layers than the shape has (both numbers are reported)")
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (no batch 1 / 64, no prefill)")
@@ -689,6 +787,8 @@ def main() -> int:
         return run_tipezen(args.steps, warmup)
     if args.workload == "dominex":
         return run_dominex(args.steps, warmup, [args.size] if args.size else None)
+    if args.workload == "sadupel":
+        return run_sadupel(args.steps, warmup, [args.size] if args.size else None)
     if args.workload != "headline":
         return run_workload(args.workload, 0 if args.layers == SHAPE["num_layers"] else args.layers)
 

@@ -137,11 +137,14 @@ def plain_expert(h, up, down):
     return relu_squared(h @ up.T) @ down.T
 
 
-def experts_mixer(h, w: Dict[str, torch.Tensor], p: str, mlp: dict):
+def experts_mixer(h, w: Dict[str, torch.Tensor], p: str, mlp: dict, round_router_input: bool = False):
+    """``round_router_input``: the router reads the bfloat16 rounding of h (the design allows either); a token whose choice
+    of experts changes with it is a close call."""
     r = mlp["router"]
     E, ident = int(r["experts"]), int(r.get("identity", 0) or 0)
     g = r.get("groups") or {}
-    idx, wts = route(h, w[p + ".router"], w[p + ".correction"], int(r["top"]), int(g.get("count", 1)), int(g.get("keep", 1)))
+    hr = h.to(torch.bfloat16).to(h.dtype) if round_router_input else h
+    idx, wts = route(hr, w[p + ".router"], w[p + ".correction"], int(r["top"]), int(g.get("count", 1)), int(g.get("keep", 1)))
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e, s in zip(idx[t].tolist(), wts[t]):
@@ -167,7 +170,8 @@ def layer_runs(config: dict) -> List[tuple]:
     return runs + [(i, None) for i in range(stop, n)]
 
 
-def forward(config: dict, weights: Dict[str, torch.Tensor], tokens, dtype=torch.float64, layers_out: Optional[list] = None):
+def forward(config: dict, weights: Dict[str, torch.Tensor], tokens, dtype=torch.float64, layers_out: Optional[list] = None,
+            round_router_input: bool = False):
     """Logits [T, vocab] of one sequence; ``layers_out`` receives the residual after every layer run."""
     w = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in weights.items()}
     eps = float(config["norm"]["eps"])
@@ -181,7 +185,7 @@ def forward(config: dict, weights: Dict[str, torch.Tensor], tokens, dtype=torch.
         h = rms_norm(x, w[p + ".norm1"], eps)
         y = attention_mixer(h, w, p + ".mix", l["mixer"], eps)
         if l.get("mlp") is not None:
-            y = y + experts_mixer(h, w, p + ".mlp", l["mlp"])
+            y = y + experts_mixer(h, w, p + ".mlp", l["mlp"], round_router_input)
         x = x + mult * y
         if layers_out is not None:
             layers_out.append(x.clone())

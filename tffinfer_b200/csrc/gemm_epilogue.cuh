@@ -11,7 +11,8 @@ namespace tc5 {
 // own tensor and k, v to the token's slot of the paged cache (epilogue_quarter_qkv below)
 // EPI_GEGLU: as EPI_SWIGLU with the tanh form of gelu on the gate, 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))),
 // which is g / (1 + exp(-2 sqrt(2/pi) (g + 0.044715 g^3))): the same exponential and division as silu
-enum Epilogue : int { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2, EPI_QKV = 3, EPI_GEGLU = 4 };
+// EPI_RELU2: a plain product stored as bfloat16 with the square of relu applied, relu(x)^2 (a feed-forward without a gate).
+enum Epilogue : int { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2, EPI_QKV = 3, EPI_GEGLU = 4, EPI_RELU2 = 5 };
 __host__ __device__ constexpr bool epi_gated(int e) { return e == EPI_SWIGLU || e == EPI_GEGLU; }
 
 // act(g) of the gated epilogues with the fast exponential and division (the result is rounded to bfloat16)
@@ -71,7 +72,12 @@ __device__ __forceinline__ void epilogue_quarter_tma(uint32_t t_addr, uint32_t m
                 } else {
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
-                        __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+                        float x0 = __uint_as_float(v[2 * j]), x1 = __uint_as_float(v[2 * j + 1]);
+                        if constexpr (EPI == EPI_RELU2) {
+                            x0 = fmaxf(x0, 0.f); x1 = fmaxf(x1, 0.f);
+                            x0 *= x0; x1 *= x1;
+                        }
+                        __nv_bfloat162 b2 = __floats2bfloat162_rn(x0, x1);
                         packed[h * 8 + j] = *reinterpret_cast<uint32_t*>(&b2);
                     }
                 }

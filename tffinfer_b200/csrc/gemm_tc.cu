@@ -428,16 +428,35 @@ TFF_API int tff_gemm_tc_gated(const void* A, const void* W, void* out, int M, in
     return gemm_tc_gated(A, W, out, M, I, K, bn, act, stream);
 }
 
+// out[M, N] = relu(A W^T)^2 as bfloat16: a plain product with the activation of a feed-forward without a gate in its
+// epilogue.  Normal orientation (prompt-sized M and decode steps above 16 rows); TFF_ERR_UNSUPPORTED for shapes it does
+// not take.  act: 2 = the square of relu.
+TFF_API int tff_gemm_tc_act(const void* A, const void* W, void* out, int M, int N, int K, int bn, int act,
+                            cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return TFF_OK;
+    if (K <= 0 || act != 2) return TFF_ERR_BAD_ARGUMENT;
+    if (K % 8 != 0 || N % 8 != 0 || (bn != 128 && bn != 256)) return TFF_ERR_UNSUPPORTED;
+    if (((uintptr_t)A & 15) || ((uintptr_t)W & 15) || ((uintptr_t)out & 15)) return TFF_ERR_UNSUPPORTED;
+    if (tff_device_error_flag() == nullptr) return TFF_ERR_LAUNCH;
+    CUtensorMap tl, tc, to;
+    if (!tff_tensor_map_2d(A, M, K, BM, BK, 2, &tl)) return TFF_ERR_DRIVER;
+    if (!tff_tensor_map_2d(W, N, K, bn, BK, 2, &tc)) return TFF_ERR_DRIVER;
+    if (!tff_tensor_map_2d(out, M, N, 32, 64, 2, &to)) return TFF_ERR_DRIVER;
+    if (bn == 256) return launch_tc<256, false, EPI_RELU2, bf16, true>(tl, tc, to, out, M, N, K, N, 0, stream);
+    return launch_tc<128, false, EPI_RELU2, bf16, true>(tl, tc, to, out, M, N, K, N, 0, stream);
+}
+
 // Grouped products on the same kernel: the rows of A ([rows, K], rows a multiple of 128) are tiles of 128 rows that
 // each belong to one group (lane_group[tile] on the device; -1: the tile is not used), W is [groups * group_rows, K],
-// and tile t is multiplied with its group's rows of W:  out[rows, group_rows] = A W_g^T, or, gated, out[rows,
+// and tile t is multiplied with its group's rows of W:  out[rows, group_rows] = A W_g^T (act 2, not gated: the square of
+// relu of it, bfloat16), or, gated, out[rows,
 // group_rows / 2] = act(A Wg_g^T) * (A Wu_g^T) with every group's gate and up rows alternating in blocks of 64 as
 // above.  The rows of a routed feed-forward's tokens, sorted by expert with every expert's share padded to 128.
 TFF_API int tff_gemm_tc_grouped(const void* A, const void* W, void* out, int out_is_bf16, int rows, int groups,
                                 int group_rows, int K, int bn, int gated, int act, const int* lane_group,
                                 cudaStream_t stream) {
     if (rows <= 0 || groups <= 0 || group_rows <= 0) return TFF_OK;
-    if (K <= 0 || !lane_group || (act != 0 && act != 1)) return TFF_ERR_BAD_ARGUMENT;
+    if (K <= 0 || !lane_group || (act != 0 && act != 1 && !(act == 2 && !gated))) return TFF_ERR_BAD_ARGUMENT;
     if (K % 8 != 0 || rows % BM != 0 || (bn != 128 && bn != 256)) return TFF_ERR_UNSUPPORTED;
     if (((uintptr_t)A & 15) || ((uintptr_t)W & 15) || ((uintptr_t)out & 15)) return TFF_ERR_UNSUPPORTED;
     if (tff_device_error_flag() == nullptr) return TFF_ERR_LAUNCH;
@@ -458,6 +477,11 @@ TFF_API int tff_gemm_tc_grouped(const void* A, const void* W, void* out, int out
     const int elt = out_is_bf16 ? 2 : 4;
     if (((long long)group_rows * elt) % 16 != 0) return TFF_ERR_UNSUPPORTED;
     if (!tff_tensor_map_2d(out, rows, group_rows, 32, 128 / elt, elt, &to)) return TFF_ERR_DRIVER;
+    if (act == 2) {                                   // not gated: the square of relu of the plain product, bfloat16
+        if (!out_is_bf16) return TFF_ERR_UNSUPPORTED;
+        if (bn == 256) return launch_tc<256, false, EPI_RELU2, bf16, true>(tl, tc, to, out, rows, group_rows, K, group_rows, 0, stream, lane_group, group_rows);
+        return launch_tc<128, false, EPI_RELU2, bf16, true>(tl, tc, to, out, rows, group_rows, K, group_rows, 0, stream, lane_group, group_rows);
+    }
     if (out_is_bf16) {
         if (bn == 256) return launch_tc<256, false, EPI_STORE, bf16, true>(tl, tc, to, out, rows, group_rows, K, group_rows, 0, stream, lane_group, group_rows);
         return launch_tc<128, false, EPI_STORE, bf16, true>(tl, tc, to, out, rows, group_rows, K, group_rows, 0, stream, lane_group, group_rows);

@@ -134,16 +134,17 @@ __global__ void last_token_kernel(const int* __restrict__ tokens, const int* __r
     if (q1 > q_start[b]) state[slots[b]] = tokens[q1 - 1];
 }
 
-// y = act(x) elementwise: 2 = the square of relu.
-template <typename T>
-__global__ void unary_act_kernel(const T* __restrict__ x, T* __restrict__ y, long long n, int act) {
+// y = act(x) elementwise: 2 = the square of relu.  clear: x is set to zero behind the read (an accumulator buffer).
+template <typename TI, typename TO>
+__global__ void unary_act_kernel(TI* x, TO* y, long long n, int act, int clear) {   // x and y may be one buffer
     pdl_launch_dependents();
     pdl_wait();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
-    float v = to_f32<T>(x[i]);
+    float v = to_f32<TI>(x[i]);
+    if (clear) x[i] = from_f32<TI>(0.f);
     if (act == 2) { v = fmaxf(v, 0.f); v = v * v; }
-    y[i] = from_f32<T>(v);
+    y[i] = from_f32<TO>(v);
 }
 
 }  // namespace
@@ -200,10 +201,16 @@ TFF_API int tff_pair_embed(const int* tokens, const int* positions, const int* t
                           slots, state, num_requests);
 }
 
-TFF_API int tff_unary_act(const void* x, void* y, int is_bf16, long long n, int act, cudaStream_t stream) {
+// x_dt, y_dt: 0 = float32, 1 = bfloat16 (float32 -> bfloat16, or the same type on both sides; in place is fine).
+TFF_API int tff_unary_act(void* x, int x_dt, void* y, int y_dt, long long n, int act, int clear, cudaStream_t stream) {
     if (n <= 0) return TFF_OK;
-    if (act != 2) return TFF_ERR_BAD_ARGUMENT;
+    if (act != 2 || (clear && x == y)) return TFF_ERR_BAD_ARGUMENT;
     const unsigned blocks = (unsigned)((n + 255) / 256);
-    if (is_bf16) return tff_launch_pdl(unary_act_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16*)x, (bf16*)y, n, act);
-    return tff_launch_pdl(unary_act_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)x, (float*)y, n, act);
+    if (x_dt == 1 && y_dt == 1)
+        return tff_launch_pdl(unary_act_kernel<bf16, bf16>, dim3(blocks), dim3(256), 0, stream, (bf16*)x, (bf16*)y, n, act, clear);
+    if (x_dt == 0 && y_dt == 1)
+        return tff_launch_pdl(unary_act_kernel<float, bf16>, dim3(blocks), dim3(256), 0, stream, (float*)x, (bf16*)y, n, act, clear);
+    if (x_dt == 0 && y_dt == 0)
+        return tff_launch_pdl(unary_act_kernel<float, float>, dim3(blocks), dim3(256), 0, stream, (float*)x, (float*)y, n, act, clear);
+    return TFF_ERR_BAD_ARGUMENT;
 }

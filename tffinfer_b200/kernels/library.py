@@ -369,14 +369,16 @@ class CudaKernels:
         return torch.stack([gate_w.view(I // b, b, K), up_w.view(I // b, b, K)], dim=1).reshape(2 * I, K).contiguous()
 
     # ------------------------------------------------------- accumulator buffers
-    def projection_buffer(self, rows: int, width: int, device, act_dtype) -> torch.Tensor:
+    def projection_buffer(self, rows: int, width: int, device, act_dtype, use: str = "") -> torch.Tensor:
         """A float32 [rows, width] buffer for a projection's accumulators.  For decode-sized bfloat16
         batches it is a persistent buffer that is zero now and that its reader sets back to zero
         (``release_input`` of qk_norm_rope_kv_write, ``clear`` of swiglu), so that the split product
-        can add into it without a clearing kernel; otherwise it is plain scratch."""
+        can add into it without a clearing kernel; otherwise it is plain scratch.  Buffers of different ``use`` are
+        different buffers: a product that runs while a sublayer's output of the same shape is still waiting for its
+        reader names a use of its own."""
         if act_dtype != torch.bfloat16 or rows > self.SWAP_MAX_M:
             return torch.empty((rows, width), dtype=torch.float32, device=device)
-        key = (rows, width, str(device))
+        key = (rows, width, str(device), use)
         buf = self._accumulators.get(key)
         if buf is None:
             buf = torch.zeros((rows, width), dtype=torch.float32, device=device)
@@ -866,20 +868,45 @@ class CudaKernels:
         self.launches += 2
 
     def unary_act(self, x, out, activation: str) -> None:
-        """out = act(x) element by element (may be in place); act "relu2": the square of relu."""
+        """out = act(x) element by element (may be in place; x float32 and out bfloat16 also); act "relu2": the square
+        of relu.  An x that is one of the accumulator buffers kept at zero between uses is cleared behind the read."""
         self._need_cuda(x, out)
-        assert x.dtype == out.dtype and x.numel() == out.numel()
-        self._check(self.lib.tff_unary_act(_ptr(x), _ptr(out), _c_int(_dt(x)), ctypes.c_longlong(x.numel()),
-                                           _c_int(self.ACTIVATION_CODES[activation]), self._stream()), "unary_act")
+        assert x.numel() == out.numel() and (x.dtype == out.dtype or x.dtype == torch.float32)
+        clear = 1 if (x.data_ptr() in self._acc_zero and x.data_ptr() != out.data_ptr()) else 0
+        self._check(self.lib.tff_unary_act(_ptr(x), _c_int(_dt(x)), _ptr(out), _c_int(_dt(out)), ctypes.c_longlong(x.numel()),
+                                           _c_int(self.ACTIVATION_CODES[activation]), _c_int(clear), self._stream()), "unary_act")
+        if clear:
+            self._acc_zero[x.data_ptr()] = True
         self.launches += 1
+
+    def gemm_act(self, a, w, out, activation: str = "relu2") -> None:
+        """out[T, N] = act(a @ w^T) for an activation of one product ("relu2").  Above CLUSTER_MAX_M rows in bfloat16 the
+        activation is applied in the tcgen05 product's epilogue; decode-sized and float32 steps run the product into
+        float32 and the activation kernel behind it."""
+        self._need_cuda(a, w, out)
+        T, N = out.shape
+        K = a.shape[1]
+        tc = (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and K % 8 == 0 and a.data_ptr() % 16 == 0
+              and w.data_ptr() % 16 == 0)
+        if tc and T > self.CLUSTER_MAX_M and N % 8 == 0 and out.dtype == torch.bfloat16 and out.data_ptr() % 16 == 0:
+            bn = self.prompt_plan(T, N, K, False, kinds=(256, 128))[1]
+            self._check(self.lib.tff_gemm_tc_act(_ptr(a), _ptr(w), _ptr(out), _c_int(T), _c_int(N), _c_int(K), _c_int(bn),
+                                                 _c_int(self.ACTIVATION_CODES[activation]), self._stream()), "gemm_tc_act")
+            self.launches += 1
+            return
+        if tc and T <= self.SWAP_MAX_M:
+            up = self.projection_buffer(T, N, out.device, out.dtype, use="act")
+        else:
+            up = torch.empty((T, N), dtype=torch.float32, device=out.device)
+        self.gemm(a, w, up)
+        self.unary_act(up, out, activation)
 
     def plain_mlp(self, h, w_up, w_down, residual, activation: str = "relu2", out=None) -> None:
         """residual += down(act(up(h))), a feed-forward without a gate; with ``residual`` None the result goes to ``out``."""
         if isinstance(h, DeferredNorm):
             h = h.materialize()
         act = torch.empty((h.shape[0], w_up.shape[0]), dtype=h.dtype, device=h.device)
-        self.gemm(h, w_up, act)
-        self.unary_act(act, act, activation)
+        self.gemm_act(h, w_up, act, activation)
         if residual is None:
             self.gemm(act, w_down, out)
         else:
@@ -956,14 +983,13 @@ class CudaKernels:
         assert tuple(w.shape) == (groups, group_rows, K) and out.shape[0] == rows
         assert out.shape[1] == (group_rows // 2 if gated else group_rows)
         bn = 256 if (group_rows % 256 == 0 and rows >= 2048) else 128
-        unary = (not gated) and activation == "relu2"
+        code = self.ACTIVATION_CODES[activation]
+        if not gated and code < 2:
+            code = 0                      # a plain product: only a function of one product ("relu2") is applied to it
         self._check(self.lib.tff_gemm_tc_grouped(_ptr(a), _ptr(w), _ptr(out), _c_int(_dt(out)), _c_int(rows), _c_int(groups),
                                                  _c_int(group_rows), _c_int(K), _c_int(bn), _c_int(1 if gated else 0),
-                                                 _c_int(self.ACTIVATION_CODES[activation] if gated else 0), _ptr(lane_group),
-                                                 self._stream()), "gemm_tc_grouped")
+                                                 _c_int(code), _ptr(lane_group), self._stream()), "gemm_tc_grouped")
         self.launches += 1
-        if unary:
-            self.unary_act(out, out, "relu2")
 
     def moe_dispatch(self, h, w_router, top: int, renormalize: bool, scale_rows: bool, tile_rows: int = 0,
                      padded_rows: int = 0, router=None):
@@ -1461,7 +1487,7 @@ class CudaKernels:
             return
         small = tc and T <= self.SWAP_MAX_M
         if small:
-            gu = self.projection_buffer(T, 2 * I, out.device, out.dtype)
+            gu = self.projection_buffer(T, 2 * I, out.device, out.dtype, use="act")
         else:
             gu = torch.empty((T, 2 * I), dtype=out.dtype, device=out.device)
         self.gemm(a, w_gate_up, gu)
