@@ -265,6 +265,60 @@ def test_hashed_pair_embedding_across_steps(ops):
         assert torch.equal(torch.cat(got[r]), table[torch.tensor(rows)]), r
 
 
+@pytest.mark.parametrize("nq,nkv,d,dv,dims,taps", [(3, 1, 24, 10, 12, 3), (4, 2, 64, 32, 64, 4), (2, 2, 16, 16, 8, 1), (8, 1, 32, 40, 32, 8)])
+def test_convolution_norm_rotation_and_cache_write_in_one_kernel(ops, nq, nkv, d, dv, dims, taps):
+    """Two requests in portions: q, the cached keys and values and the gates against the plain convolution, whole norm and
+    rotation; widths that take the four-channel loads and widths that do not."""
+    from tffinfer_b200.parts.position import ScaledRotary
+    g = torch.Generator().manual_seed(nq + taps)
+    widths = (nq * d, nkv * d, nkv * dv)
+    C, eps, page, base, factor = sum(widths), 1e-5, 8, 1e4, 2.0
+    ld = -(-(C + nq) // 8) * 8
+    lens = {"x": 21, "y": 6}
+    u = {r: torch.randn(n, ld, generator=g) for r, n in lens.items()}
+    cw = [torch.randn(w, taps, generator=g) for w in widths]
+    nw = [1 + 0.3 * torch.randn(w, generator=g) for w in widths[:2]]
+    part = ScaledRotary(dims, base, "halves", None, factor)
+    part.prepare(ops, "cuda", 0)
+    want = {}
+    for r, n in lens.items():
+        y = [P.causal_conv(u[r][:, o:o + w].double(), cw[i].double()) for i, (o, w) in
+             enumerate(zip((0, widths[0], widths[0] + widths[1]), widths))]
+        pos = torch.arange(n)
+        q = P.rotate_halves(P.rms_norm(y[0], nw[0].double(), eps).view(n, nq, d), pos, base, dims, factor)
+        k = P.rotate_halves(P.rms_norm(y[1], nw[1].double(), eps).view(n, nkv, d), pos, base, dims, factor)
+        want[r] = (q, k, y[2].view(n, nkv, dv), torch.sigmoid(u[r][:, C:C + nq].double()))
+    state = torch.full((3, max(taps - 1, 1), C), float("nan"), device="cuda") if taps > 1 else None
+    dc = max(d, dv)
+    cache = torch.full((8, 1, 2, nkv, page, dc), float("nan"), device="cuda")
+    tables = {"x": [5, 0, 3], "y": [6, -1, -1]}
+    slot, done = {"x": 2, "y": 0}, {"x": 0, "y": 0}
+    got_q, got_g = {r: torch.empty(n, nq, d) for r, n in lens.items()}, {r: torch.empty(n, nq) for r, n in lens.items()}
+    for step in ({"x": 2, "y": 1}, {"x": 1}, {"y": 5, "x": 13}, {"x": 5}):
+        live = list(step)
+        b = fake_batch([step[r] for r in live], [done[r] for r in live], "cuda", page, slots=[slot[r] for r in live])
+        table = torch.tensor([tables[r] for r in live], dtype=torch.int32, device="cuda")
+        rows = torch.cat([u[r][done[r]:done[r] + step[r]] for r in live]).cuda()
+        q = torch.empty(rows.shape[0], nq * d, device="cuda")
+        gates = torch.empty(rows.shape[0], nq, device="cuda")
+        ops.conv_finish(rows, [w.cuda() for w in cw], [w.cuda() for w in nw], taps, eps, state, q, part.frequencies(), b,
+                        table, cache, 0, page, nq, nkv, d, dv, C, gates)
+        ops.short_conv_state(rows, taps, C, state, b)
+        row = 0
+        for r in live:
+            got_q[r][done[r]:done[r] + step[r]] = q[row:row + step[r]].cpu().view(-1, nq, d)
+            got_g[r][done[r]:done[r] + step[r]] = gates[row:row + step[r]].cpu()
+            row += step[r]
+            done[r] += step[r]
+    for r, n in lens.items():
+        q, k, v, gate = want[r]
+        assert torch.allclose(got_q[r].double(), q, rtol=1e-4, atol=1e-4), float((got_q[r].double() - q).abs().max())
+        assert torch.allclose(got_g[r].double(), gate, atol=1e-6)
+        for p in range(n):
+            at = cache[tables[r][p // page], 0, :, :, p % page].cpu().double()
+            assert torch.allclose(at[0, :, :d], k[p], rtol=1e-4, atol=1e-4) and torch.allclose(at[1, :, :dv], v[p], rtol=1e-4, atol=1e-4), (r, p)
+
+
 def _sink_case(ops, dtype, d, dv, lens, starts, aim, sink_value, softcap=0.0, page=16, nq=4, nkv=2):
     """The query of request 0's last token is aimed at the key ``aim`` positions back with a score that dwarfs the
     others, so that its output is that key's value if the key is seen; the learned sinks take their share."""

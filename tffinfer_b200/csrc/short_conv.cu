@@ -134,6 +134,133 @@ __global__ void last_token_kernel(const int* __restrict__ tokens, const int* __r
     if (q1 > q_start[b]) state[slots[b]] = tokens[q1 - 1];
 }
 
+// The convolution and the norms above and what lies between them and the token mixing, in one pass over a token's row:
+// one block a token keeps the convolved q, k and v of the token in shared memory (C floats), norms q and k there, rotates
+// the first rot_dims dimensions of every q and k head by the token's position (pairs (2i, 2i+1) or (i, i + rot_dims/2),
+// angle float(position) * freq[i], cos and sin times ``magnitude``), stores q to q_out [T, nq*d], k and v to the token's
+// slot of the paged cache ([pages, layers, 2, kv heads, page, dc]) and sigmoid(proj[t, gate_off + h]) to gate_out.  The
+// float32 row of convolved values is never written to memory.  proj is only read: short_conv_state runs behind it.
+template <typename TQ, typename TC>
+__global__ void __launch_bounds__(256)
+conv_finish_kernel(const float* __restrict__ proj, int ld, ConvSegs segs, int taps, int C,
+                   const float* __restrict__ state, const int* __restrict__ positions, const int* __restrict__ tok_req,
+                   const int* __restrict__ q_start, const int* __restrict__ slots, float eps,
+                   TQ* __restrict__ q_out, const float* __restrict__ freq, int rot_dims, float magnitude, int interleaved,
+                   const int* __restrict__ block_table, int table_width, TC* __restrict__ cache, KvLayout L, int layer,
+                   int dc, int gate_off, float* __restrict__ gate_out, int nq, int nkv, int d, int dv) {
+    extern __shared__ float y_s[];                           // C floats, 32 for the sums, rot_dims for cos and sin
+    float* red = y_s + C;
+    float* cos_s = red + 32;
+    float* sin_s = cos_s + (rot_dims >> 1);
+    __shared__ float rs_s[MAX_SEGS];
+    const int t = blockIdx.x;
+    const int b = tok_req[t];
+    const int pos = positions[t];
+    const int i_in = t - q_start[b];
+    for (int i = threadIdx.x; i < (rot_dims >> 1); i += 256) {   // the token's angles once, for all heads
+        float sn, cs;
+        sincosf((float)pos * freq[i], &sn, &cs);
+        cos_s[i] = cs * magnitude; sin_s[i] = sn * magnitude;
+    }
+    const float* st = state + (size_t)slots[b] * (taps - 1) * C;
+    const bool vec = (ld & 3) == 0 && (C & 3) == 0 && (((size_t)proj | (size_t)state) & 15) == 0;
+    for (int s = 0; s < segs.n; ++s) {
+        const int off = segs.off[s], width = segs.width[s];
+        float ss = 0.f;
+        if (vec && (off & 3) == 0 && (width & 3) == 0) {     // four neighbouring channels a thread
+            for (int c = threadIdx.x * 4; c < width; c += 1024) {
+                float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (segs.w[s]) {
+                    const float* wc = segs.w[s] + (size_t)c * taps;
+                    for (int j = 0; j < taps; ++j) {
+                        const int back = taps - 1 - j;
+                        if (back > pos) continue;
+                        const float* src = back <= i_in ? proj + (size_t)(t - back) * ld + off + c
+                                                        : st + (size_t)(taps - 1 - (back - i_in)) * C + off + c;
+                        const float4 u = *reinterpret_cast<const float4*>(src);
+                        y.x = fmaf(wc[j], u.x, y.x);
+                        y.y = fmaf(wc[taps + j], u.y, y.y);
+                        y.z = fmaf(wc[2 * taps + j], u.z, y.z);
+                        y.w = fmaf(wc[3 * taps + j], u.w, y.w);
+                    }
+                } else {
+                    y = *reinterpret_cast<const float4*>(proj + (size_t)t * ld + off + c);
+                }
+                *reinterpret_cast<float4*>(y_s + off + c) = y;
+                ss = fmaf(y.x, y.x, ss); ss = fmaf(y.y, y.y, ss); ss = fmaf(y.z, y.z, ss); ss = fmaf(y.w, y.w, ss);
+            }
+        } else {
+            for (int c = threadIdx.x; c < width; c += 256) {
+                float y;
+                if (segs.w[s]) {
+                    y = 0.f;
+                    const float* wc = segs.w[s] + (size_t)c * taps;
+                    for (int j = 0; j < taps; ++j) {
+                        const int back = taps - 1 - j;
+                        if (back > pos) continue;
+                        const float u = back <= i_in ? proj[(size_t)(t - back) * ld + off + c]
+                                                     : st[(size_t)(taps - 1 - (back - i_in)) * C + off + c];
+                        y = fmaf(wc[j], u, y);
+                    }
+                } else {
+                    y = proj[(size_t)t * ld + off + c];
+                }
+                y_s[off + c] = y;
+                ss = fmaf(y, y, ss);
+            }
+        }
+        if (segs.norm[s]) {                                  // uniform over the block
+            ss = block_sum<256>(ss, red);
+            if (threadIdx.x == 0) rs_s[s] = rsqrtf(ss / (float)width + eps);
+            __syncthreads();                                 // red is used again
+        } else if (threadIdx.x == 0) {
+            rs_s[s] = 1.f;
+        }
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int half = rot_dims >> 1;
+    const size_t page_at = (size_t)b * table_width + pos / L.page_size;
+    const int page = block_table[page_at];
+    for (int head = warp; head < nq + 2 * nkv; head += 8) {
+        const bool is_q = head < nq, is_k = !is_q && head < nq + nkv;
+        TC* slot = nullptr;
+        if (!is_q) {
+            if (page < 0) continue;                           // no page: the host never schedules this
+            const int kvh = is_k ? head - nq : head - nq - nkv;
+            slot = cache + (size_t)page * L.page_stride + (size_t)layer * L.layer_stride + (is_k ? 0 : L.kv_stride) +
+                   (size_t)kvh * L.head_stride + (size_t)(pos % L.page_size) * dc;
+        }
+        if (!is_q && !is_k) {                                 // a value head: as it left the convolution
+            const float* src = y_s + segs.off[2] + (size_t)(head - nq - nkv) * dv;
+            for (int i = lane; i < dv; i += 32) slot[i] = from_f32<TC>(src[i]);
+            continue;
+        }
+        const int s = is_q ? 0 : 1;
+        const int col = is_q ? head * d : (head - nq) * d;    // within the segment
+        const float* src = y_s + segs.off[s] + col;
+        const float* nw = segs.norm[s] ? segs.norm[s] + col : nullptr;
+        const float rs = rs_s[s];
+        TQ* qrow = q_out + (size_t)t * nq * d + (size_t)head * d;
+        for (int i = lane; i < half; i += 32) {
+            const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
+            const float a = nw ? (src[ia] * rs) * nw[ia] : src[ia], bb = nw ? (src[ib] * rs) * nw[ib] : src[ib];
+            const float sn = sin_s[i], cs = cos_s[i];
+            const float ra = a * cs - bb * sn, rb = bb * cs + a * sn;
+            if (is_q) { qrow[ia] = from_f32<TQ>(ra); qrow[ib] = from_f32<TQ>(rb); }
+            else { slot[ia] = from_f32<TC>(ra); slot[ib] = from_f32<TC>(rb); }
+        }
+        for (int i = 2 * half + lane; i < d; i += 32) {
+            const float a = nw ? (src[i] * rs) * nw[i] : src[i];
+            if (is_q) qrow[i] = from_f32<TQ>(a);
+            else slot[i] = from_f32<TC>(a);
+        }
+    }
+    if (gate_out)
+        for (int h = threadIdx.x; h < nq; h += 256)
+            gate_out[(size_t)t * nq + h] = 1.0f / (1.0f + expf(-proj[(size_t)t * ld + gate_off + h]));
+}
+
 // y = act(x) elementwise: 2 = the square of relu.  clear: x is set to zero behind the read (an accumulator buffer).
 template <typename TI, typename TO>
 __global__ void unary_act_kernel(TI* x, TO* y, long long n, int act, int clear) {   // x and y may be one buffer
@@ -172,6 +299,48 @@ TFF_API int tff_short_conv_norm(const float* proj, int ld, float* out, int num_s
     short_conv_norm_kernel<<<num_tokens, 256, 0, stream>>>(proj, ld, out, segs, taps, C, state, positions, tok_req,
                                                            q_start, slots, eps);
     return tff_launch_status();
+}
+
+// short_conv_norm and qkv_finish in one kernel, for three segments q (nq*d), k (nkv*d), v (nkv*dv) with a paged cache:
+// q_dt, cache_dt: 0 = float32, 1 = bfloat16.  TFF_ERR_UNSUPPORTED when a token's channels do not fit shared memory.
+TFF_API int tff_conv_finish(const float* proj, int ld, const float* const* seg_w, const float* const* seg_norm, int taps,
+                            float eps, const float* state, const int* positions, const int* tok_req, const int* q_start,
+                            const int* slots, void* q_out, int q_dt, const float* freq, int rot_dims, float magnitude,
+                            int interleaved, const int* block_table, int table_width, void* cache, int cache_dt,
+                            int cache_layers, int layer, int page_size, int dc, int gate_off, float* gate_out,
+                            int num_tokens, int nq, int nkv, int d, int dv, cudaStream_t stream) {
+    if (num_tokens <= 0) return TFF_OK;
+    if (!proj || !q_out || !cache || !block_table || taps < 1 || taps > MAX_TAPS || nq <= 0 || nkv <= 0 || d <= 0 || dv <= 0 ||
+        rot_dims < 0 || rot_dims > d || (rot_dims & 1) || page_size <= 0 || dc < d || dc < dv)
+        return TFF_ERR_BAD_ARGUMENT;
+    if ((rot_dims > 0 && !freq) || (taps > 1 && !state) || (gate_out && gate_off < 0)) return TFF_ERR_BAD_ARGUMENT;
+    ConvSegs segs;
+    segs.n = 3;
+    const int widths[3] = {nq * d, nkv * d, nkv * dv};
+    int C = 0;
+    for (int s = 0; s < 3; ++s) {
+        segs.off[s] = C; segs.width[s] = widths[s]; segs.w[s] = seg_w[s]; segs.norm[s] = s < 2 ? seg_norm[s] : nullptr;
+        C += widths[s];
+    }
+    if (C > ld || (gate_out && gate_off + nq > ld)) return TFF_ERR_BAD_ARGUMENT;
+    const size_t smem = (size_t)(C + 32 + rot_dims) * sizeof(float);
+    if (smem > 200 * 1024) return TFF_ERR_UNSUPPORTED;
+    const KvLayout L = make_kv_layout(cache_layers, nkv, page_size, dc);
+#define TFF_CF(TQ, TC)                                                                                                \
+    do {                                                                                                              \
+        if (smem > 48 * 1024 &&                                                                                       \
+            cudaFuncSetAttribute(conv_finish_kernel<TQ, TC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
+            return TFF_ERR_LAUNCH;                                                                                    \
+        conv_finish_kernel<TQ, TC><<<num_tokens, 256, smem, stream>>>(proj, ld, segs, taps, C, state, positions, tok_req, q_start, \
+            slots, eps, (TQ*)q_out, freq, rot_dims, magnitude, interleaved, block_table, table_width, (TC*)cache, L, layer, dc,  \
+            gate_off, gate_out, nq, nkv, d, dv);                                                                      \
+        return tff_launch_status();                                                                                   \
+    } while (0)
+    if (q_dt == 0 && cache_dt == 0) TFF_CF(float, float);
+    if (q_dt == 1 && cache_dt == 1) TFF_CF(bf16, bf16);
+    if (q_dt == 0 && cache_dt == 1) TFF_CF(float, bf16);
+#undef TFF_CF
+    return TFF_ERR_BAD_ARGUMENT;
 }
 
 TFF_API int tff_short_conv_state(float* proj, int ld, int clear, int taps, int C, float* state, const int* q_start,

@@ -575,6 +575,14 @@ class CudaKernels:
             conv = pre.get("conv") or (None, None, None)
             norm = pre.get("norm") or (None, None)
             widths = (nq * d, nkv * d, nkv * dv)
+            if v_mode == 0 and self.CONV_FINISH and (sum(widths) + 32 + d) * 4 <= 200 * 1024:
+                # convolution, norms, rotation, cache write and gates in one pass over the accumulators
+                self.conv_finish(proj, conv, norm, taps, float(pre.get("eps", 0.0)), pre.get("state"), q, freq, batch,
+                                 block_table, kv_cache, kv_layer, page_size, nq, nkv, d, dv, gate_off, gates)
+                self.short_conv_state(proj, taps, sum(widths), pre.get("state"), batch)
+                self.attention_ext(q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, dv, scale,
+                                   window, softcap, sink, gates)
+                return
             mixed = torch.empty((T, proj.shape[1]), dtype=torch.float32, device=proj.device)
             self.short_conv_norm(proj, mixed, [(widths[0], conv[0], norm[0]), (widths[1], conv[1], norm[1]),
                                                (widths[2], conv[2], None)], taps, float(pre.get("eps", 0.0)),
@@ -833,6 +841,40 @@ class CudaKernels:
                                                  _c_int(taps), _c_float(eps), _ptr(state), _ptr(batch.positions),
                                                  _ptr(batch.tok_req), _ptr(batch.q_start), _ptr(batch.slots), _c_int(T),
                                                  self._stream()), "short_conv_norm")
+        self.launches += 1
+
+    CONV_FINISH = os.environ.get("TFFINFER_CONV_FINISH", "1") != "0"   # 0: the convolution and the finish as two kernels
+
+    def conv_finish(self, proj, conv, norm, taps: int, eps: float, state, q_out, freq, batch, block_table, kv_cache,
+                    kv_layer, page_size, nq, nkv, d, dv, gate_off: int = -1, gate_out=None) -> None:
+        """short_conv_norm and qkv_finish in one kernel (csrc/short_conv.cu conv_finish_kernel): the float32 rows ``proj``
+        [T, ld] = [q | k | v | gates ...] are convolved over time (``conv`` = three float32 [width, taps] or None), q and k
+        normed over their whole width (``norm`` = two float32 [width] or None), rotated (``freq`` as for qkv_finish) and
+        stored: q to ``q_out`` [T, nq*d], k and v to the tokens' cache slots, the sigmoid of the gates to ``gate_out``.
+        ``proj`` is left as it is: short_conv_state, behind it, keeps the rows the next step needs and clears them."""
+        self._need_cuda(proj, q_out, state, block_table, gate_out)
+        T, ld = proj.shape
+        assert proj.dtype == torch.float32 and kv_cache is not None and tuple(kv_cache.shape[2:5]) == (2, nkv, page_size)
+        widths = (nq * d, nkv * d, nkv * dv)
+        for width, cw in zip(widths, conv):
+            self._need_cuda(cw)
+            assert cw is None or (cw.dtype == torch.float32 and tuple(cw.shape) == (width, taps))
+        for width, nw in zip(widths, norm):
+            self._need_cuda(nw)
+            assert nw is None or (nw.dtype == torch.float32 and nw.numel() == width)
+        if taps > 1:
+            assert state is not None and state.dtype == torch.float32 and tuple(state.shape[1:]) == (taps - 1, sum(widths))
+        f, rot, mag, inter = freq if freq is not None else (None, 0, 1.0, False)
+        c_ptr, _, c_layers, c_layer = self._cache_args(kv_cache, kv_layer)
+        convs = (_vp * 3)(*[cw.data_ptr() if cw is not None else None for cw in conv])
+        norms = (_vp * 2)(*[nw.data_ptr() if nw is not None else None for nw in norm])
+        self._check(self.lib.tff_conv_finish(
+            _ptr(proj), _c_int(ld), convs, norms, _c_int(taps), _c_float(eps), _ptr(state), _ptr(batch.positions),
+            _ptr(batch.tok_req), _ptr(batch.q_start), _ptr(batch.slots), _ptr(q_out), _c_int(_dt(q_out)), _ptr(f), _c_int(rot),
+            _c_float(mag), _c_int(1 if inter else 0), _ptr(block_table), _c_int(block_table.shape[1]), c_ptr,
+            _c_int(_dt(kv_cache)), _c_int(c_layers), _c_int(c_layer), _c_int(page_size), _c_int(kv_cache.shape[-1]),
+            _c_int(gate_off), _ptr(gate_out), _c_int(T), _c_int(nq), _c_int(nkv), _c_int(d), _c_int(dv), self._stream()),
+            "conv_finish")
         self.launches += 1
 
     def short_conv_state(self, proj, taps: int, channels: int, state, batch) -> None:
