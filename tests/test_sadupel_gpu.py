@@ -301,7 +301,7 @@ def test_convolution_norm_rotation_and_cache_write_in_one_kernel(ops, nq, nkv, d
         rows = torch.cat([u[r][done[r]:done[r] + step[r]] for r in live]).cuda()
         q = torch.empty(rows.shape[0], nq * d, device="cuda")
         gates = torch.empty(rows.shape[0], nq, device="cuda")
-        ops.conv_finish(rows, [w.cuda() for w in cw], [w.cuda() for w in nw], taps, eps, state, q, part.frequencies(), b,
+        ops.conv_finish(rows, [w.t().contiguous().cuda() for w in cw], [w.cuda() for w in nw], taps, eps, state, q, part.frequencies(), b,
                         table, cache, 0, page, nq, nkv, d, dv, C, gates)
         ops.short_conv_state(rows, taps, C, state, b)
         row = 0

@@ -134,22 +134,64 @@ __global__ void last_token_kernel(const int* __restrict__ tokens, const int* __r
     if (q1 > q_start[b]) state[slots[b]] = tokens[q1 - 1];
 }
 
+// Two neighbouring elements in one store (the address is a multiple of the pair's size).
+__device__ __forceinline__ void store_pair(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+__device__ __forceinline__ void store_pair(bf16* p, float a, float b) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
+
+// One q or k head of conv_finish_kernel, by one warp: (y * rs) * w for every element (w null: y as it is), the first
+// 2 * half elements rotated, stored to dst.  src, w, cos_s, sin_s are shared memory.  pairs: two elements a lane and
+// store (every size involved is even and dst is aligned for it).
+template <typename T>
+__device__ __forceinline__ void finish_head(T* __restrict__ dst, const float* src, const float* w, float rs,
+                                            const float* cos_s, const float* sin_s, int half, int d, int interleaved,
+                                            bool pairs, int lane) {
+    auto val = [&](int i) { return w ? (src[i] * rs) * w[i] : src[i]; };
+    if (pairs && !interleaved) {
+        for (int i = lane * 2; i < half; i += 64) {
+            const float a0 = val(i), a1 = val(i + 1), b0 = val(i + half), b1 = val(i + half + 1);
+            const float c0 = cos_s[i], c1 = cos_s[i + 1], s0 = sin_s[i], s1 = sin_s[i + 1];
+            store_pair(dst + i, a0 * c0 - b0 * s0, a1 * c1 - b1 * s1);
+            store_pair(dst + i + half, b0 * c0 + a0 * s0, b1 * c1 + a1 * s1);
+        }
+    } else {
+        for (int i = lane; i < half; i += 32) {
+            const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
+            const float a = val(ia), bb = val(ib);
+            const float sn = sin_s[i], cs = cos_s[i];
+            const float ra = a * cs - bb * sn, rb = bb * cs + a * sn;
+            if (pairs) store_pair(dst + ia, ra, rb);           // interleaved: the two are neighbours
+            else { dst[ia] = from_f32<T>(ra); dst[ib] = from_f32<T>(rb); }
+        }
+    }
+    if (pairs) for (int i = 2 * half + lane * 2; i < d; i += 64) store_pair(dst + i, val(i), val(i + 1));
+    else for (int i = 2 * half + lane; i < d; i += 32) dst[i] = from_f32<T>(val(i));
+}
+
 // The convolution and the norms above and what lies between them and the token mixing, in one pass over a token's row:
 // one block a token keeps the convolved q, k and v of the token in shared memory (C floats), norms q and k there, rotates
 // the first rot_dims dimensions of every q and k head by the token's position (pairs (2i, 2i+1) or (i, i + rot_dims/2),
 // angle float(position) * freq[i], cos and sin times ``magnitude``), stores q to q_out [T, nq*d], k and v to the token's
 // slot of the paged cache ([pages, layers, 2, kv heads, page, dc]) and sigmoid(proj[t, gate_off + h]) to gate_out.  The
 // float32 row of convolved values is never written to memory.  proj is only read: short_conv_state runs behind it.
-template <typename TQ, typename TC>
-__global__ void __launch_bounds__(256)
+// Here the convolution's weights are TRANSPOSED, segs.w[s] = [taps, width], so that one load brings a tap's weights of
+// four neighbouring channels.  A block waits for memory as seldom as it can: everything that does not depend on
+// anything computed here is loaded ahead of the first wait (all taps of a thread's channels, the norm weights, which go
+// to shared memory beside the channels, the page number, the gates); behind the sums of squares only shared memory is read.
+// MT: the most taps this instance holds in registers (4 or MAX_TAPS).
+template <typename TQ, typename TC, int MT>
+__global__ void __launch_bounds__(256, MT <= 4 ? 3 : 2)
 conv_finish_kernel(const float* __restrict__ proj, int ld, ConvSegs segs, int taps, int C,
                    const float* __restrict__ state, const int* __restrict__ positions, const int* __restrict__ tok_req,
                    const int* __restrict__ q_start, const int* __restrict__ slots, float eps,
                    TQ* __restrict__ q_out, const float* __restrict__ freq, int rot_dims, float magnitude, int interleaved,
                    const int* __restrict__ block_table, int table_width, TC* __restrict__ cache, KvLayout L, int layer,
-                   int dc, int gate_off, float* __restrict__ gate_out, int nq, int nkv, int d, int dv) {
-    extern __shared__ float y_s[];                           // C floats, 32 for the sums, rot_dims for cos and sin
-    float* red = y_s + C;
+                   int dc, int gate_off, float* __restrict__ gate_out, int nq, int nkv, int d, int dv, int pairs) {
+    extern __shared__ float y_s[];          // C channels, the norm weights of q and k, 32 for the sums, cos and sin
+    const int NW = segs.off[2];             // q and k lie first
+    float* nw_s = y_s + C;
+    float* red = nw_s + NW;
     float* cos_s = red + 32;
     float* sin_s = cos_s + (rot_dims >> 1);
     __shared__ float rs_s[MAX_SEGS];
@@ -157,50 +199,79 @@ conv_finish_kernel(const float* __restrict__ proj, int ld, ConvSegs segs, int ta
     const int b = tok_req[t];
     const int pos = positions[t];
     const int i_in = t - q_start[b];
+    const int slot_no = slots[b];
+    const int page = block_table[(size_t)b * table_width + pos / L.page_size];
+    if (gate_out)
+        for (int h = threadIdx.x; h < nq; h += 256)
+            gate_out[(size_t)t * nq + h] = 1.0f / (1.0f + expf(-proj[(size_t)t * ld + gate_off + h]));
     for (int i = threadIdx.x; i < (rot_dims >> 1); i += 256) {   // the token's angles once, for all heads
         float sn, cs;
         sincosf((float)pos * freq[i], &sn, &cs);
         cos_s[i] = cs * magnitude; sin_s[i] = sn * magnitude;
     }
-    const float* st = state + (size_t)slots[b] * (taps - 1) * C;
-    const bool vec = (ld & 3) == 0 && (C & 3) == 0 && (((size_t)proj | (size_t)state) & 15) == 0;
-    for (int s = 0; s < segs.n; ++s) {
-        const int off = segs.off[s], width = segs.width[s];
-        float ss = 0.f;
-        if (vec && (off & 3) == 0 && (width & 3) == 0) {     // four neighbouring channels a thread
-            for (int c = threadIdx.x * 4; c < width; c += 1024) {
-                float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (segs.w[s]) {
-                    const float* wc = segs.w[s] + (size_t)c * taps;
-                    for (int j = 0; j < taps; ++j) {
-                        const int back = taps - 1 - j;
-                        if (back > pos) continue;
-                        const float* src = back <= i_in ? proj + (size_t)(t - back) * ld + off + c
-                                                        : st + (size_t)(taps - 1 - (back - i_in)) * C + off + c;
-                        const float4 u = *reinterpret_cast<const float4*>(src);
-                        y.x = fmaf(wc[j], u.x, y.x);
-                        y.y = fmaf(wc[taps + j], u.y, y.y);
-                        y.z = fmaf(wc[2 * taps + j], u.z, y.z);
-                        y.w = fmaf(wc[3 * taps + j], u.w, y.w);
+    const float* st = state + (size_t)slot_no * (taps - 1) * C;
+    // Four neighbouring channels a thread in ONE pass over all three segments when every border is a multiple of four.
+    bool flat = ((ld | C | segs.off[1] | segs.off[2]) & 3) == 0 && (((size_t)proj | (size_t)state) & 15) == 0;
+    for (int s = 0; s < 3; ++s) flat = flat && (((size_t)segs.w[s] | (size_t)segs.norm[s]) & 15) == 0;
+    if (flat) {
+        float ss0 = 0.f, ss1 = 0.f;
+        for (int c = threadIdx.x * 4; c < C; c += 1024) {
+            const int s = c >= segs.off[2] ? 2 : (c >= segs.off[1] ? 1 : 0);
+            const int cs = c - segs.off[s];
+            float4 y;
+            if (segs.norm[s]) *reinterpret_cast<float4*>(nw_s + c) = *reinterpret_cast<const float4*>(segs.norm[s] + cs);
+            if (segs.w[s]) {
+                float4 u[MT], w[MT];
+#pragma unroll
+                for (int j = 0; j < MT; ++j) {
+                    u[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    w[j] = u[j];
+                    const int back = taps - 1 - j;
+                    if (j < taps && back <= pos) {               // zeros before the sequence's start
+                        const float* src = back <= i_in ? proj + (size_t)(t - back) * ld + c
+                                                        : st + (size_t)(taps - 1 - (back - i_in)) * C + c;
+                        u[j] = *reinterpret_cast<const float4*>(src);
+                        w[j] = *reinterpret_cast<const float4*>(segs.w[s] + (size_t)j * segs.width[s] + cs);
                     }
-                } else {
-                    y = *reinterpret_cast<const float4*>(proj + (size_t)t * ld + off + c);
                 }
-                *reinterpret_cast<float4*>(y_s + off + c) = y;
-                ss = fmaf(y.x, y.x, ss); ss = fmaf(y.y, y.y, ss); ss = fmaf(y.z, y.z, ss); ss = fmaf(y.w, y.w, ss);
+                y = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int j = 0; j < MT; ++j) {
+                    y.x = fmaf(w[j].x, u[j].x, y.x);
+                    y.y = fmaf(w[j].y, u[j].y, y.y);
+                    y.z = fmaf(w[j].z, u[j].z, y.z);
+                    y.w = fmaf(w[j].w, u[j].w, y.w);
+                }
+            } else {
+                y = *reinterpret_cast<const float4*>(proj + (size_t)t * ld + c);
             }
-        } else {
+            *reinterpret_cast<float4*>(y_s + c) = y;
+            float ss = y.x * y.x;
+            ss = fmaf(y.y, y.y, ss); ss = fmaf(y.z, y.z, ss); ss = fmaf(y.w, y.w, ss);
+            if (s == 0) ss0 += ss; else if (s == 1) ss1 += ss;
+        }
+        if (segs.norm[0]) ss0 = block_sum<256>(ss0, red);      // uniform over the block
+        if (segs.norm[1]) { __syncthreads(); ss1 = block_sum<256>(ss1, red); }
+        if (threadIdx.x == 0) {
+            rs_s[0] = segs.norm[0] ? rsqrtf(ss0 / (float)segs.width[0] + eps) : 1.f;
+            rs_s[1] = segs.norm[1] ? rsqrtf(ss1 / (float)segs.width[1] + eps) : 1.f;
+            rs_s[2] = 1.f;
+        }
+    } else {
+        for (int s = 0; s < segs.n; ++s) {
+            const int off = segs.off[s], width = segs.width[s];
+            float ss = 0.f;
             for (int c = threadIdx.x; c < width; c += 256) {
                 float y;
+                if (segs.norm[s]) nw_s[off + c] = segs.norm[s][c];
                 if (segs.w[s]) {
                     y = 0.f;
-                    const float* wc = segs.w[s] + (size_t)c * taps;
                     for (int j = 0; j < taps; ++j) {
                         const int back = taps - 1 - j;
                         if (back > pos) continue;
                         const float u = back <= i_in ? proj[(size_t)(t - back) * ld + off + c]
                                                      : st[(size_t)(taps - 1 - (back - i_in)) * C + off + c];
-                        y = fmaf(wc[j], u, y);
+                        y = fmaf(segs.w[s][(size_t)j * width + c], u, y);
                     }
                 } else {
                     y = proj[(size_t)t * ld + off + c];
@@ -208,20 +279,18 @@ conv_finish_kernel(const float* __restrict__ proj, int ld, ConvSegs segs, int ta
                 y_s[off + c] = y;
                 ss = fmaf(y, y, ss);
             }
-        }
-        if (segs.norm[s]) {                                  // uniform over the block
-            ss = block_sum<256>(ss, red);
-            if (threadIdx.x == 0) rs_s[s] = rsqrtf(ss / (float)width + eps);
-            __syncthreads();                                 // red is used again
-        } else if (threadIdx.x == 0) {
-            rs_s[s] = 1.f;
+            if (segs.norm[s]) {                                  // uniform over the block
+                ss = block_sum<256>(ss, red);
+                if (threadIdx.x == 0) rs_s[s] = rsqrtf(ss / (float)width + eps);
+                __syncthreads();                                 // red is used again
+            } else if (threadIdx.x == 0) {
+                rs_s[s] = 1.f;
+            }
         }
     }
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int half = rot_dims >> 1;
-    const size_t page_at = (size_t)b * table_width + pos / L.page_size;
-    const int page = block_table[page_at];
     for (int head = warp; head < nq + 2 * nkv; head += 8) {
         const bool is_q = head < nq, is_k = !is_q && head < nq + nkv;
         TC* slot = nullptr;
@@ -233,32 +302,17 @@ conv_finish_kernel(const float* __restrict__ proj, int ld, ConvSegs segs, int ta
         }
         if (!is_q && !is_k) {                                 // a value head: as it left the convolution
             const float* src = y_s + segs.off[2] + (size_t)(head - nq - nkv) * dv;
-            for (int i = lane; i < dv; i += 32) slot[i] = from_f32<TC>(src[i]);
+            if (pairs) for (int i = lane * 2; i < dv; i += 64) store_pair(slot + i, src[i], src[i + 1]);
+            else for (int i = lane; i < dv; i += 32) slot[i] = from_f32<TC>(src[i]);
             continue;
         }
         const int s = is_q ? 0 : 1;
-        const int col = is_q ? head * d : (head - nq) * d;    // within the segment
-        const float* src = y_s + segs.off[s] + col;
-        const float* nw = segs.norm[s] ? segs.norm[s] + col : nullptr;
-        const float rs = rs_s[s];
-        TQ* qrow = q_out + (size_t)t * nq * d + (size_t)head * d;
-        for (int i = lane; i < half; i += 32) {
-            const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
-            const float a = nw ? (src[ia] * rs) * nw[ia] : src[ia], bb = nw ? (src[ib] * rs) * nw[ib] : src[ib];
-            const float sn = sin_s[i], cs = cos_s[i];
-            const float ra = a * cs - bb * sn, rb = bb * cs + a * sn;
-            if (is_q) { qrow[ia] = from_f32<TQ>(ra); qrow[ib] = from_f32<TQ>(rb); }
-            else { slot[ia] = from_f32<TC>(ra); slot[ib] = from_f32<TC>(rb); }
-        }
-        for (int i = 2 * half + lane; i < d; i += 32) {
-            const float a = nw ? (src[i] * rs) * nw[i] : src[i];
-            if (is_q) qrow[i] = from_f32<TQ>(a);
-            else slot[i] = from_f32<TC>(a);
-        }
+        const int col = segs.off[s] + (is_q ? head * d : (head - nq) * d);
+        const float* w = segs.norm[s] ? nw_s + col : nullptr;
+        if (is_q) finish_head<TQ>(q_out + (size_t)t * nq * d + (size_t)head * d, y_s + col, w, rs_s[0], cos_s, sin_s, half,
+                                  d, interleaved, pairs != 0, lane);
+        else finish_head<TC>(slot, y_s + col, w, rs_s[1], cos_s, sin_s, half, d, interleaved, pairs != 0, lane);
     }
-    if (gate_out)
-        for (int h = threadIdx.x; h < nq; h += 256)
-            gate_out[(size_t)t * nq + h] = 1.0f / (1.0f + expf(-proj[(size_t)t * ld + gate_off + h]));
 }
 
 // y = act(x) elementwise: 2 = the square of relu.  clear: x is set to zero behind the read (an accumulator buffer).
@@ -301,7 +355,8 @@ TFF_API int tff_short_conv_norm(const float* proj, int ld, float* out, int num_s
     return tff_launch_status();
 }
 
-// short_conv_norm and qkv_finish in one kernel, for three segments q (nq*d), k (nkv*d), v (nkv*dv) with a paged cache:
+// short_conv_norm and qkv_finish in one kernel, for three segments q (nq*d), k (nkv*d), v (nkv*dv) with a paged cache;
+// seg_w are the convolution's weights TRANSPOSED, [taps, width]:
 // q_dt, cache_dt: 0 = float32, 1 = bfloat16.  TFF_ERR_UNSUPPORTED when a token's channels do not fit shared memory.
 TFF_API int tff_conv_finish(const float* proj, int ld, const float* const* seg_w, const float* const* seg_norm, int taps,
                             float eps, const float* state, const int* positions, const int* tok_req, const int* q_start,
@@ -323,22 +378,30 @@ TFF_API int tff_conv_finish(const float* proj, int ld, const float* const* seg_w
         C += widths[s];
     }
     if (C > ld || (gate_out && gate_off + nq > ld)) return TFF_ERR_BAD_ARGUMENT;
-    const size_t smem = (size_t)(C + 32 + rot_dims) * sizeof(float);
+    const size_t smem = (size_t)(C + widths[0] + widths[1] + 32 + rot_dims) * sizeof(float);
     if (smem > 200 * 1024) return TFF_ERR_UNSUPPORTED;
+    // two elements a store where every head, rotated part and cache row starts on an even element of an aligned buffer
+    const int pairs = (((rot_dims >> 1) | d | dv | dc) & 1) == 0 && (((size_t)q_out | (size_t)cache) & 7) == 0 ? 1 : 0;
     const KvLayout L = make_kv_layout(cache_layers, nkv, page_size, dc);
-#define TFF_CF(TQ, TC)                                                                                                \
+#define TFF_CF(TQ, TC, MT)                                                                                               \
     do {                                                                                                              \
         if (smem > 48 * 1024 &&                                                                                       \
-            cudaFuncSetAttribute(conv_finish_kernel<TQ, TC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
+            cudaFuncSetAttribute(conv_finish_kernel<TQ, TC, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
             return TFF_ERR_LAUNCH;                                                                                    \
-        conv_finish_kernel<TQ, TC><<<num_tokens, 256, smem, stream>>>(proj, ld, segs, taps, C, state, positions, tok_req, q_start, \
+        conv_finish_kernel<TQ, TC, MT><<<num_tokens, 256, smem, stream>>>(proj, ld, segs, taps, C, state, positions, tok_req, q_start, \
             slots, eps, (TQ*)q_out, freq, rot_dims, magnitude, interleaved, block_table, table_width, (TC*)cache, L, layer, dc,  \
-            gate_off, gate_out, nq, nkv, d, dv);                                                                      \
+            gate_off, gate_out, nq, nkv, d, dv, pairs);                                                               \
         return tff_launch_status();                                                                                   \
     } while (0)
-    if (q_dt == 0 && cache_dt == 0) TFF_CF(float, float);
-    if (q_dt == 1 && cache_dt == 1) TFF_CF(bf16, bf16);
-    if (q_dt == 0 && cache_dt == 1) TFF_CF(float, bf16);
+    if (taps <= 4) {
+        if (q_dt == 0 && cache_dt == 0) TFF_CF(float, float, 4);
+        if (q_dt == 1 && cache_dt == 1) TFF_CF(bf16, bf16, 4);
+        if (q_dt == 0 && cache_dt == 1) TFF_CF(float, bf16, 4);
+    } else {
+        if (q_dt == 0 && cache_dt == 0) TFF_CF(float, float, MAX_TAPS);
+        if (q_dt == 1 && cache_dt == 1) TFF_CF(bf16, bf16, MAX_TAPS);
+        if (q_dt == 0 && cache_dt == 1) TFF_CF(float, bf16, MAX_TAPS);
+    }
 #undef TFF_CF
     return TFF_ERR_BAD_ARGUMENT;
 }

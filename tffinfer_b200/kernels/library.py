@@ -575,9 +575,10 @@ class CudaKernels:
             conv = pre.get("conv") or (None, None, None)
             norm = pre.get("norm") or (None, None)
             widths = (nq * d, nkv * d, nkv * dv)
-            if v_mode == 0 and self.CONV_FINISH and (sum(widths) + 32 + d) * 4 <= 200 * 1024:
+            if v_mode == 0 and self.CONV_FINISH and (sum(widths) + widths[0] + widths[1] + 32 + d) * 4 <= 200 * 1024:
                 # convolution, norms, rotation, cache write and gates in one pass over the accumulators
-                self.conv_finish(proj, conv, norm, taps, float(pre.get("eps", 0.0)), pre.get("state"), q, freq, batch,
+                conv_t = pre.get("conv_t") or tuple(w.t().contiguous() if w is not None else None for w in conv)
+                self.conv_finish(proj, conv_t, norm, taps, float(pre.get("eps", 0.0)), pre.get("state"), q, freq, batch,
                                  block_table, kv_cache, kv_layer, page_size, nq, nkv, d, dv, gate_off, gates)
                 self.short_conv_state(proj, taps, sum(widths), pre.get("state"), batch)
                 self.attention_ext(q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, dv, scale,
@@ -848,7 +849,8 @@ class CudaKernels:
     def conv_finish(self, proj, conv, norm, taps: int, eps: float, state, q_out, freq, batch, block_table, kv_cache,
                     kv_layer, page_size, nq, nkv, d, dv, gate_off: int = -1, gate_out=None) -> None:
         """short_conv_norm and qkv_finish in one kernel (csrc/short_conv.cu conv_finish_kernel): the float32 rows ``proj``
-        [T, ld] = [q | k | v | gates ...] are convolved over time (``conv`` = three float32 [width, taps] or None), q and k
+        [T, ld] = [q | k | v | gates ...] are convolved over time (``conv`` = three float32 [taps, width], the weights
+        transposed so that a tap's weights of neighbouring channels lie together, or None), q and k
         normed over their whole width (``norm`` = two float32 [width] or None), rotated (``freq`` as for qkv_finish) and
         stored: q to ``q_out`` [T, nq*d], k and v to the tokens' cache slots, the sigmoid of the gates to ``gate_out``.
         ``proj`` is left as it is: short_conv_state, behind it, keeps the rows the next step needs and clears them."""
@@ -858,7 +860,7 @@ class CudaKernels:
         widths = (nq * d, nkv * d, nkv * dv)
         for width, cw in zip(widths, conv):
             self._need_cuda(cw)
-            assert cw is None or (cw.dtype == torch.float32 and tuple(cw.shape) == (width, taps))
+            assert cw is None or (cw.dtype == torch.float32 and tuple(cw.shape) == (taps, width) and cw.is_contiguous())
         for width, nw in zip(widths, norm):
             self._need_cuda(nw)
             assert nw is None or (nw.dtype == torch.float32 and nw.numel() == width)

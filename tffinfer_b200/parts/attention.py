@@ -145,7 +145,7 @@ class GatedSinkAttention(Mixer):
         self.v_width = self.num_kv_heads * self.v_head_dim
         self.cache_dim = max(self.head_dim, self.v_head_dim)     # a cache slot holds a key or a value
         self.w_in = self.w_o = self.lam = self.sink_w = None
-        self.conv_w = self.norm_w = None
+        self.conv_w = self.conv_wt = self.norm_w = None
 
     def cache_need(self):
         kv = KVNeed(self.num_kv_heads, self.cache_dim, self.window)
@@ -192,6 +192,7 @@ class GatedSinkAttention(Mixer):
             self.sink_w = tensors[n["sink"]].to(torch.float32).contiguous()
         if self.conv_taps > 0:
             self.conv_w = tuple(tensors[n[w]].to(torch.float32).contiguous() for w in ("q_conv", "k_conv", "v_conv"))
+            self.conv_wt = tuple(w.t().contiguous() for w in self.conv_w)     # [taps, channels]: the fused kernel's layout
         if self.qk_norm == "whole":
             self.norm_w = (tensors[n["q_norm"]].to(torch.float32).contiguous(), tensors[n["k_norm"]].to(torch.float32).contiguous())
 
@@ -211,7 +212,7 @@ class GatedSinkAttention(Mixer):
         attn = torch.empty((T, self.num_heads * self.v_head_dim), dtype=h.dtype, device=h.device)
         pre = None
         if self.conv_taps > 0 or self.qk_norm == "whole":
-            pre = dict(taps=max(self.conv_taps, 1), conv=self.conv_w, norm=self.norm_w, eps=self.qk_norm_eps,
+            pre = dict(taps=max(self.conv_taps, 1), conv=self.conv_w, conv_t=self.conv_wt, norm=self.norm_w, eps=self.qk_norm_eps,
                        state=ctx.state if self.conv_taps > 1 else None)
         ops.attend_gated(h, self.w_in, freq, batch, ctx.block_table, ctx.kv_cache, ctx.kv_layer, ctx.page_size, attn,
                          self.num_heads, self.num_kv_heads, self.head_dim, self.v_head_dim, self.scale, self.window,
