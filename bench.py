@@ -690,6 +690,8 @@ def run_sadupel(steps: int, warmup: int, sizes=None) -> int:
     peaks = load_peaks()
     steps = min(steps, 32)
     P = PROMPT_LEN
+    clocks = ClockSampler()            # over the whole run: SM clock at the median, the throttle reasons seen
+    clocks.start()
     for size in (sizes or SADUPEL_SIZES):
         W, H, G, D, TAPS, E, IDENT, TOP, GROUPS, KEEP, F, SF = SADUPEL_SIZES[size]
         for model, make in (("sadupel", sadupel_engine), ("dominex", dominex_engine)):
@@ -736,7 +738,11 @@ def run_sadupel(steps: int, warmup: int, sizes=None) -> int:
                     fr["prefill_attention_tflops"] = round(attn_flops / (k["attention_bf16"][1] / 1e3) / 1e12, 2)
                 kd = kinds.get("decode") or {}
                 if "gemm_grouped" in kd:
-                    w_b = nl * min(E, 8 * TOP) * 2 * W * F * 2
+                    # the experts a step of 8 tokens touches: with random weights every choice is one of E + IDENT outputs,
+                    # so of the E experts with tensors about E * (1 - (1 - TOP / outputs)^8) are read
+                    touched = E * (1.0 - (1.0 - TOP / float(E + IDENT)) ** 8)
+                    w_b = nl * touched * 2 * W * F * 2
+                    fr["decode_experts_touched"] = round(touched, 1)
                     fr["decode_gemm_grouped_hbm_frac"] = round(w_b / (kd["gemm_grouped"][1] / 1e3) / 1e9 / peaks["hbm_gbs"], 4)
                 if "attention_bf16" in kd:
                     cache_b = nl * 8 * P * 2 * G * D * 2
@@ -745,6 +751,8 @@ def run_sadupel(steps: int, warmup: int, sizes=None) -> int:
             print(json.dumps(line), flush=True)
             del engine
             torch.cuda.empty_cache()
+    clocks.stop()
+    print(json.dumps({"point": "clocks", "clocks": clocks.summary()}), flush=True)
     return 0
 
 

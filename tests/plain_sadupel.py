@@ -115,20 +115,30 @@ def attention_mixer(h, w: Dict[str, torch.Tensor], p: str, m: dict, eps: float, 
     return o.reshape(T, H * Dv) @ w[p + ".o"].T
 
 
-def route(h, w_router, correction, top: int, groups: int, keep: int):
+def route(h, w_router, correction, top: int, groups: int, keep: int, margin_out: Optional[list] = None):
     """Scores s = softmax(W_r h) over all router outputs; choice scores s + correction; only the ``keep`` groups (of
     ``groups`` equal groups of neighbours) with the largest best choice score stay eligible; the ``top`` largest choice
-    scores among them are chosen (the lower index wins a tie); the weights are the chosen s.  -> (index [T, top], s [T, top])"""
+    scores among them are chosen (the lower index wins a tie); the weights are the chosen s.  -> (index [T, top], s [T, top]).
+    ``margin_out`` receives a [T] tensor: how far the choice is from another one, the smaller of the gap between the last
+    chosen and the first unchosen choice score and the gap between the last kept and the first dropped group."""
     s = torch.softmax(h @ w_router.T, dim=-1)
     c = s + correction[None, :]
     T, E = c.shape
+    margin = torch.full((T,), float("inf"), dtype=c.dtype)
     if groups > 1 and keep < groups:
         per = E // groups
         best = c.reshape(T, groups, per).max(dim=-1).values
+        ranked = torch.sort(best, dim=-1, descending=True).values
+        margin = ranked[:, keep - 1] - ranked[:, keep]
         order = torch.sort(best, dim=-1, descending=True, stable=True).indices[:, :keep]
         ok = torch.zeros((T, groups), dtype=torch.bool)
         ok.scatter_(1, order, True)
         c = c.masked_fill(~ok[:, :, None].expand(T, groups, per).reshape(T, E), float("-inf"))
+    if top < E:
+        ranked = torch.sort(c, dim=-1, descending=True).values
+        margin = torch.minimum(margin, ranked[:, top - 1] - ranked[:, top])
+    if margin_out is not None:
+        margin_out.append(margin)
     idx = torch.sort(c, dim=-1, descending=True, stable=True).indices[:, :top]
     return idx, torch.gather(s, 1, idx)
 
@@ -137,14 +147,16 @@ def plain_expert(h, up, down):
     return relu_squared(h @ up.T) @ down.T
 
 
-def experts_mixer(h, w: Dict[str, torch.Tensor], p: str, mlp: dict, round_router_input: bool = False):
+def experts_mixer(h, w: Dict[str, torch.Tensor], p: str, mlp: dict, round_router_input: bool = False,
+                  margin_out: Optional[list] = None):
     """``round_router_input``: the router reads the bfloat16 rounding of h (the design allows either); a token whose choice
     of experts changes with it is a close call."""
     r = mlp["router"]
     E, ident = int(r["experts"]), int(r.get("identity", 0) or 0)
     g = r.get("groups") or {}
     hr = h.to(torch.bfloat16).to(h.dtype) if round_router_input else h
-    idx, wts = route(hr, w[p + ".router"], w[p + ".correction"], int(r["top"]), int(g.get("count", 1)), int(g.get("keep", 1)))
+    idx, wts = route(hr, w[p + ".router"], w[p + ".correction"], int(r["top"]), int(g.get("count", 1)), int(g.get("keep", 1)),
+                     margin_out)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e, s in zip(idx[t].tolist(), wts[t]):
@@ -171,8 +183,9 @@ def layer_runs(config: dict) -> List[tuple]:
 
 
 def forward(config: dict, weights: Dict[str, torch.Tensor], tokens, dtype=torch.float64, layers_out: Optional[list] = None,
-            round_router_input: bool = False):
-    """Logits [T, vocab] of one sequence; ``layers_out`` receives the residual after every layer run."""
+            round_router_input: bool = False, margins_out: Optional[list] = None):
+    """Logits [T, vocab] of one sequence; ``layers_out`` receives the residual after every layer run, ``margins_out`` a
+    [T] tensor per routed layer run (see route)."""
     w = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in weights.items()}
     eps = float(config["norm"]["eps"])
     mult = float(config.get("residual_mult", 1.0))
@@ -185,7 +198,7 @@ def forward(config: dict, weights: Dict[str, torch.Tensor], tokens, dtype=torch.
         h = rms_norm(x, w[p + ".norm1"], eps)
         y = attention_mixer(h, w, p + ".mix", l["mixer"], eps)
         if l.get("mlp") is not None:
-            y = y + experts_mixer(h, w, p + ".mlp", l["mlp"], round_router_input)
+            y = y + experts_mixer(h, w, p + ".mlp", l["mlp"], round_router_input, margins_out)
         x = x + mult * y
         if layers_out is not None:
             layers_out.append(x.clone())

@@ -102,7 +102,7 @@ def test_random_model_folder_runs_in_the_plain_implementation(tmp_path):
     assert "l0.mix.sink" in str(e.value)
 
 
-@pytest.mark.parametrize("base,dims,factor", [(1e4, 64, 1.0), (2.5e5, 32, 2.0), (500.0, 6, 16.0)])
+@pytest.mark.parametrize("base,dims,factor", [(1e4, 64, 1.0), (3e5, 32, 2.5), (500.0, 6, 16.0)])
 def test_frequencies_match_the_plain_ones(base, dims, factor):
     from tffinfer_b200.parts.model import build_part
     desc = tff.get_architecture("Sadupel").describe(SadupelConfig(

@@ -48,13 +48,13 @@ def config(name: str) -> SadupelConfig:
         m = moe(32, 7, 4, identity=3, groups=5, keep=5, shared=0)
         layers = (att(8, 2, 16, 8, 8, 0.5, 12.0, 1e6, 16, 8.0, m), att(2, 1, 128, 128, 3, 0.09, 50.0, 1e4, 64, 1.0, m))
         return SadupelConfig("Sadupel", vocab_size=264, hidden_size=64, norm_eps=1e-6, residual_mult=0.7,
-                             bigram=(1000, 1, 1), loop=(0, 2, 3), layers=layers)
+                             bigram=(1000, 1, 1), loop=(0, 2, 4), layers=layers)
     if name == "d":      # one group kept of many, top == the group's size; a loop of one pass at the end
         c = config("c")
         m = moe(24, 9, 3, identity=3, groups=4, keep=1, shared=40)
         layers = tuple(SadupelLayer(**{**l.__dict__, "mlp": m}) for l in c.layers) + (c.layers[0],)
         return SadupelConfig("Sadupel", vocab_size=c.vocab_size, hidden_size=c.hidden_size, norm_eps=c.norm_eps,
-                             residual_mult=0.3, bigram=(17, 3, 11), loop=(2, 3, 1), layers=layers)
+                             residual_mult=0.35, bigram=(17, 3, 11), loop=(2, 3, 1), layers=layers)
     raise KeyError(name)
 
 
@@ -97,6 +97,9 @@ def plain_logits(cj, sd, reqs, dtype):
     for r, t in reqs.items():
         want = P.forward(cj, sd, t)
         close = None
+        if dtype == "float32":                 # the bar of every position (see assert_close)
+            mine = P.forward(cj, sd, t, dtype=torch.float32).double()
+            close = (3.0 * (mine - want).abs().amax(dim=-1) / want.abs().amax(dim=-1)).clamp_min(TOL[dtype])
         if dtype == "bfloat16":
             other = P.forward(cj, sd, t, round_router_input=True)
             close = ((other - want).abs() / want.abs().amax(dim=-1, keepdim=True)).amax(dim=-1) > TOL[dtype] / 2
@@ -110,8 +113,14 @@ def assert_close(got, want, dtype, what):
     under a quarter of it: a fault of a kernel, the cache or a state moves most positions."""
     want, close = want if isinstance(want, tuple) else (want, None)
     if dtype == "float32":
-        bad = first_bad(got, want, TOL[dtype])
-        assert bad is None, f"{what}: token {bad[0]} off by {bad[1]:.3g}"
+        if close is None:
+            bad = first_bad(got, want, TOL[dtype])
+            assert bad is None, f"{what}: token {bad[0]} off by {bad[1]:.3g}"
+            return
+        assert int((close > TOL[dtype]).sum()) <= 1 + close.numel() // 50, f"{what}: too many ill-conditioned positions for a test"
+        err = torch.nan_to_num((got.double() - want).abs().amax(dim=-1) / want.abs().amax(dim=-1), nan=float("inf"))
+        bad = torch.nonzero(err > close)
+        assert bad.numel() == 0, f"{what}: token {int(bad[0])} off by {float(err[int(bad[0])]):.3g} (bar {float(close[int(bad[0])]):.3g})"
         return
     scale = want.abs().amax(dim=-1, keepdim=True).clamp_min(1e-30)
     err = torch.nan_to_num(((got.double() - want.double()).abs() / scale).amax(dim=-1), nan=float("inf"))

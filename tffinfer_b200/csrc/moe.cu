@@ -18,30 +18,97 @@
 
 namespace {
 
+constexpr int ROUTE_TOK = 4;                   // tokens a block of moe_route_kernel, one warp each for the choice
+constexpr int ROUTE_THREADS = 256;
+
 template <typename TH, typename TW>
-__global__ void __launch_bounds__(128)
-moe_route_kernel(const TH* __restrict__ h, const TW* __restrict__ w_router, int W, int E, int top, int renormalize,
+__global__ void __launch_bounds__(ROUTE_THREADS)
+moe_route_kernel(const TH* __restrict__ h, const TW* __restrict__ w_router, int T, int W, int E, int top, int renormalize,
                  int softmax_scores, const float* __restrict__ correction, int groups, int keep, int num_real,
                  int* __restrict__ pair_expert, float* __restrict__ pair_weight, int* __restrict__ counts) {
-    extern __shared__ float sm[];              // W floats: the token's row; E: the scores; E: the choice scores; E: groups
-    float* row = sm;
-    float* score = sm + W;
-    float* choice = score + E;
-    float* gbest = choice + E;
+    // A block takes ROUTE_TOK tokens: the router's rows are read once for all of them (2,048 tokens re-read a 64 KB router
+    // 2,048 times otherwise), every token keeps sums of its own, and behind the products warp i does token i's choice.
+    extern __shared__ float sm[];              // per token W floats (its row) and 3 E: the scores, the choice scores, groups
     pdl_launch_dependents();
     pdl_wait();
-    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int i = threadIdx.x; i < W; i += 128) row[i] = to_f32<TH>(h[(size_t)t * W + i]);
+    const int t0 = blockIdx.x * ROUTE_TOK, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nt = min(ROUTE_TOK, T - t0);
+    float* rows = sm;                          // [ROUTE_TOK][W]
+    float* scores = sm + (size_t)ROUTE_TOK * W;   // [ROUTE_TOK][3 E]
+    if ((W & 7) == 0 && ((size_t)h & 15) == 0) {           // eight elements a load (sixteen bytes of bfloat16)
+        for (int v = threadIdx.x; v < nt * (W >> 3); v += ROUTE_THREADS) {
+            const int k = v / (W >> 3), i = (v - k * (W >> 3)) << 3;
+            float* dst = rows + (size_t)k * W + i;
+            const TH* src = h + (size_t)(t0 + k) * W + i;
+            if constexpr (sizeof(TH) == 2) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(src);
+                const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+                const float2 a = __bfloat1622float2(p2[0]), b = __bfloat1622float2(p2[1]);
+                const float2 c = __bfloat1622float2(p2[2]), d = __bfloat1622float2(p2[3]);
+                *reinterpret_cast<float4*>(dst) = make_float4(a.x, a.y, b.x, b.y);
+                *reinterpret_cast<float4*>(dst + 4) = make_float4(c.x, c.y, d.x, d.y);
+            } else {
+                *reinterpret_cast<float4*>(dst) = *reinterpret_cast<const float4*>(src);
+                *reinterpret_cast<float4*>(dst + 4) = *reinterpret_cast<const float4*>(src + 4);
+            }
+        }
+    } else {
+        for (int k = 0; k < nt; ++k)
+            for (int i = threadIdx.x; i < W; i += ROUTE_THREADS) rows[(size_t)k * W + i] = to_f32<TH>(h[(size_t)(t0 + k) * W + i]);
+    }
+    for (int k = nt; k < ROUTE_TOK; ++k)
+        for (int i = threadIdx.x; i < W; i += ROUTE_THREADS) rows[(size_t)k * W + i] = 0.f;
     __syncthreads();
-    for (int e = warp; e < E; e += 4) {
+    // A warp an output; a lane takes eight neighbouring elements a load where the rows allow it (16-byte loads, several in
+    // flight), else one.  Either way the order of a dot product's additions is fixed by W alone.
+    const bool wide = (W & 7) == 0 && ((size_t)w_router & 15) == 0;
+    for (int e = warp; e < E; e += ROUTE_THREADS / 32) {
         const TW* wr = w_router + (size_t)e * W;
-        float acc = 0.f;
-        for (int i = lane; i < W; i += 32) acc = fmaf(row[i], to_f32<TW>(wr[i]), acc);
-        acc = warp_sum(acc);
-        if (lane == 0) score[e] = softmax_scores ? acc : 1.0f / (1.0f + expf(-acc));
+        float acc[ROUTE_TOK];
+#pragma unroll
+        for (int k = 0; k < ROUTE_TOK; ++k) acc[k] = 0.f;
+        if (wide) {
+#pragma unroll 4
+            for (int i = lane * 8; i < W; i += 256) {
+                float w8[8];
+                if constexpr (sizeof(TW) == 2) {
+                    const uint4 raw = *reinterpret_cast<const uint4*>(wr + i);
+                    const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) { const float2 f = __bfloat1622float2(p2[k]); w8[2 * k] = f.x; w8[2 * k + 1] = f.y; }
+                } else {
+                    const float4 a = *reinterpret_cast<const float4*>(wr + i), b = *reinterpret_cast<const float4*>(wr + i + 4);
+                    w8[0] = a.x; w8[1] = a.y; w8[2] = a.z; w8[3] = a.w; w8[4] = b.x; w8[5] = b.y; w8[6] = b.z; w8[7] = b.w;
+                }
+#pragma unroll
+                for (int k = 0; k < ROUTE_TOK; ++k) {
+                    const float* row = rows + (size_t)k * W + i;
+                    const float4 r0 = *reinterpret_cast<const float4*>(row), r1 = *reinterpret_cast<const float4*>(row + 4);
+                    float a = acc[k];
+                    a = fmaf(r0.x, w8[0], a); a = fmaf(r0.y, w8[1], a); a = fmaf(r0.z, w8[2], a); a = fmaf(r0.w, w8[3], a);
+                    a = fmaf(r1.x, w8[4], a); a = fmaf(r1.y, w8[5], a); a = fmaf(r1.z, w8[6], a); a = fmaf(r1.w, w8[7], a);
+                    acc[k] = a;
+                }
+            }
+        } else {
+            for (int i = lane; i < W; i += 32) {
+                const float wv = to_f32<TW>(wr[i]);
+#pragma unroll
+                for (int k = 0; k < ROUTE_TOK; ++k) acc[k] = fmaf(rows[(size_t)k * W + i], wv, acc[k]);
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < ROUTE_TOK; ++k) {
+            const float z = warp_sum(acc[k]);
+            if (lane == 0) scores[(size_t)k * 3 * E + e] = softmax_scores ? z : 1.0f / (1.0f + expf(-z));
+        }
     }
     __syncthreads();
-    if (warp != 0) return;
+    if (warp >= nt) return;                    // warp i: token t0 + i
+    const int t = t0 + warp;
+    float* score = scores + (size_t)warp * 3 * E;
+    float* choice = score + E;
+    float* gbest = choice + E;
     if (softmax_scores) {                      // over all router outputs, in an order that E alone fixes
         float m = -INFINITY;
         for (int e = lane; e < E; e += 32) m = fmaxf(m, score[e]);
@@ -203,14 +270,14 @@ TFF_API int tff_moe_route(const void* h, int h_dt, const void* w_router, int w_d
     if (W <= 0 || E <= 0 || top <= 0 || top > E || !h || !w_router || num_real < 0 || num_real > E)
         return TFF_ERR_BAD_ARGUMENT;
     if (groups > 1 && (E % groups != 0 || keep <= 0 || keep > groups || top > keep * (E / groups))) return TFF_ERR_BAD_ARGUMENT;
-    const size_t smem = (size_t)(W + 3 * E) * sizeof(float);
+    const size_t smem = (size_t)ROUTE_TOK * (W + 3 * E) * sizeof(float);
     if (smem > 200 * 1024) return TFF_ERR_UNSUPPORTED;
 #define TFF_ROUTE(TH, TW)                                                                                             \
     do {                                                                                                              \
         if (smem > 48 * 1024)                                                                                         \
             cudaFuncSetAttribute(moe_route_kernel<TH, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
-        return tff_launch_pdl(moe_route_kernel<TH, TW>, dim3(T), dim3(128), smem, stream, (const TH*)h,               \
-                              (const TW*)w_router, W, E, top, renormalize, softmax_scores, correction, groups, keep, \
+        return tff_launch_pdl(moe_route_kernel<TH, TW>, dim3((T + ROUTE_TOK - 1) / ROUTE_TOK), dim3(ROUTE_THREADS), smem, stream, (const TH*)h, \
+                              (const TW*)w_router, T, W, E, top, renormalize, softmax_scores, correction, groups, keep, \
                               num_real, pair_expert, pair_weight, counts);         \
     } while (0)
     if (h_dt == 0 && w_dt == 0) TFF_ROUTE(float, float);

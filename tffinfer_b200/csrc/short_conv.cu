@@ -78,6 +78,8 @@ __global__ void __launch_bounds__(256)
 short_conv_state_kernel(float* __restrict__ proj, int ld, int clear, int taps, int C, float* __restrict__ state,
                         const int* __restrict__ q_start, const int* __restrict__ pos_start,
                         const int* __restrict__ slots) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int b = blockIdx.x;
     const int c = blockIdx.y * 256 + threadIdx.x;
     if (c >= ld) return;
@@ -195,6 +197,8 @@ conv_finish_kernel(const float* __restrict__ proj, int ld, ConvSegs segs, int ta
     float* cos_s = red + 32;
     float* sin_s = cos_s + (rot_dims >> 1);
     __shared__ float rs_s[MAX_SEGS];
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int b = tok_req[t];
     const int pos = positions[t];
@@ -388,10 +392,9 @@ TFF_API int tff_conv_finish(const float* proj, int ld, const float* const* seg_w
         if (smem > 48 * 1024 &&                                                                                       \
             cudaFuncSetAttribute(conv_finish_kernel<TQ, TC, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
             return TFF_ERR_LAUNCH;                                                                                    \
-        conv_finish_kernel<TQ, TC, MT><<<num_tokens, 256, smem, stream>>>(proj, ld, segs, taps, C, state, positions, tok_req, q_start, \
-            slots, eps, (TQ*)q_out, freq, rot_dims, magnitude, interleaved, block_table, table_width, (TC*)cache, L, layer, dc,  \
-            gate_off, gate_out, nq, nkv, d, dv, pairs);                                                               \
-        return tff_launch_status();                                                                                   \
+        return tff_launch_pdl(conv_finish_kernel<TQ, TC, MT>, dim3(num_tokens), dim3(256), smem, stream, proj, ld, segs, taps, C, \
+            state, positions, tok_req, q_start, slots, eps, (TQ*)q_out, freq, rot_dims, magnitude, interleaved, block_table,  \
+            table_width, (TC*)cache, L, layer, dc, gate_off, gate_out, nq, nkv, d, dv, pairs);                           \
     } while (0)
     if (taps <= 4) {
         if (q_dt == 0 && cache_dt == 0) TFF_CF(float, float, 4);
@@ -411,8 +414,8 @@ TFF_API int tff_short_conv_state(float* proj, int ld, int clear, int taps, int C
     if (num_requests <= 0 || (taps <= 1 && !clear)) return TFF_OK;
     if (!proj || C > ld || taps > MAX_TAPS || (taps > 1 && !state)) return TFF_ERR_BAD_ARGUMENT;
     dim3 grid(num_requests, (ld + 255) / 256);
-    short_conv_state_kernel<<<grid, 256, 0, stream>>>(proj, ld, clear, taps, taps > 1 ? C : 0, state, q_start, pos_start, slots);
-    return tff_launch_status();
+    return tff_launch_pdl(short_conv_state_kernel, grid, dim3(256), 0, stream, proj, ld, clear, taps, taps > 1 ? C : 0, state,
+                          q_start, pos_start, slots);
 }
 
 TFF_API int tff_pair_embed(const int* tokens, const int* positions, const int* tok_req, const int* q_start,
