@@ -183,7 +183,7 @@ __device__ __forceinline__ void finish_head(T* __restrict__ dst, const float* sr
 // to shared memory beside the channels, the page number, the gates); behind the sums of squares only shared memory is read.
 // MT: the most taps this instance holds in registers (4 or MAX_TAPS).
 template <typename TQ, typename TC, int MT>
-__global__ void __launch_bounds__(256, MT <= 4 ? 3 : 2)
+__global__ void __launch_bounds__(256, MT <= 4 ? 4 : 2)
 conv_finish_kernel(const float* __restrict__ proj, int ld, ConvSegs segs, int taps, int C,
                    const float* __restrict__ state, const int* __restrict__ positions, const int* __restrict__ tok_req,
                    const int* __restrict__ q_start, const int* __restrict__ slots, float eps,
