@@ -8,7 +8,8 @@
 // * visibility: causal, and optionally a sliding window (keys p-window+1 .. p) and/or blocks of ``chunk``
 //   positions counted from position 0 of the sequence (key n is seen from p only if n / chunk == p / chunk);
 // * score(p, n) = (q . k_n) * scale * temp[h]  -  r1[h] * ln(1 + r2[h] * (p - n)), with per-head float32 arrays temp
-//   (null: 1) and r1, r2 (null: no distance term);
+//   (null: 1) and r1, r2 (null: no distance term); with ``softcap`` > 0 the scaled product is first squashed to
+//   softcap * tanh(. / softcap);
 // * the output is multiplied by out_scale and may go to a column block of a wider row (out_ld, out_off).
 //
 // A tile is ROWS packed rows of one request and one key/value head: row r of the request is (token r / G, query head
@@ -17,6 +18,7 @@
 // is in, on how the prompt was cut or on what else is in the batch.  Keys outside the tile's range are never read
 // (pages behind a window may have been given back).
 #include "common.cuh"
+#include "attention_common.h"
 #include <stdlib.h>
 
 namespace {
@@ -29,6 +31,7 @@ struct TileArgs {
     int slot, page_size;
     int nq, nkv, d, dv;
     float scale; int window, chunk;
+    float softcap;                                  // > 0: a scaled score s becomes softcap * tanh(s / softcap)
     const float* temp; const float* r1; const float* r2;
     float out_scale; int q_ld, out_ld, out_off;
     int splits; float* part_o; float* part_ml;     // splits > 1: shares of the key range, merged by a second kernel
@@ -135,6 +138,7 @@ attention_tile_kernel(const TQ* __restrict__ q, const TC* __restrict__ cache, TQ
             auto score = [&](float dot, float sc, float r1, float r2, int p, int lo, int n) -> float {
                 if (p < 0 || n > p || n < lo) return -INFINITY;
                 float s = dot * sc;
+                if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
                 if (biased) s -= r1 * log1pf(r2 * (float)(p - n));
                 return s;
             };
@@ -433,6 +437,7 @@ attention_tile_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ c
             auto score = [&](float dot, float sc, float r1, float r2, int p, int lo, int n) -> float {
                 if (p < 0 || n > p || n < lo) return -INFINITY;
                 float s = dot * sc;
+                if (a.softcap > 0.f) s = a.softcap * attn_tanh(s / a.softcap);
                 if (biased) s -= r1 * log1pf(r2 * (float)(p - n));
                 return s;
             };
@@ -591,7 +596,7 @@ TFF_API int tff_attention_tile(
     void* out, int out_ld, int out_off, int num_requests, int max_q_len, int nq, int nkv, int d, int dv, float scale,
     int window, int chunk, const float* temp, const float* r1, const float* r2, float out_scale,
     int num_tokens, int splits, float* part_o, float* part_ml,
-    const void* k_dense, const void* v_dense, int k_ld, int v_ld, cudaStream_t stream) {
+    const void* k_dense, const void* v_dense, int k_ld, int v_ld, float softcap, cudaStream_t stream) {
     if (num_requests <= 0 || max_q_len <= 0) return TFF_OK;
     if ((k_dense == nullptr) != (v_dense == nullptr)) return TFF_ERR_BAD_ARGUMENT;
     if (k_dense) { planes = 2; slot = d > dv ? d : dv; page_size = 1; }      // no cache is read: any consistent geometry
@@ -603,6 +608,7 @@ TFF_API int tff_attention_tile(
     a.page_stride = page_stride; a.head_stride = (long long)page_size * slot;
     a.v_offset = planes == 2 ? (long long)nkv * page_size * slot : 0;
     a.slot = slot; a.page_size = page_size; a.nq = nq; a.nkv = nkv; a.d = d; a.dv = dv; a.scale = scale;
+    a.softcap = softcap > 0.f ? softcap : 0.f;
     a.window = window; a.chunk = chunk; a.temp = temp; a.r1 = r1; a.r2 = r2; a.out_scale = out_scale;
     a.q_ld = q_ld; a.out_ld = out_ld; a.out_off = out_off;
     if (splits < 1 || (splits > 1 && (!part_o || !part_ml))) return TFF_ERR_BAD_ARGUMENT;

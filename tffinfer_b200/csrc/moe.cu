@@ -1,7 +1,8 @@
 // The small kernels around a routed feed-forward (mixture of experts); the experts' products are gemm_grouped.cu.
 //
 //   route    per token: z = W_r h in float32 (one warp per expert, a fixed order of additions), s = sigmoid(z) or
-//            softmax(z) over all outputs, choice scores s + correction, optionally only the experts of the best
+//            softmax(z) over all outputs (or z itself, the chosen then weighted by a softmax among themselves; z may
+//            carry a bias), choice scores s + correction, optionally only the experts of the best
 //            ``keep`` of ``groups`` groups of neighbours (a group's score is its best choice score), the ``top`` experts
 //            of largest choice score (the lower index wins a tie), weights s, optionally renormalised to sum 1; writes
 //            the pair (token, k) -> (expert, weight) and counts the pairs of every expert.  The last router outputs may
@@ -23,8 +24,8 @@ constexpr int ROUTE_THREADS = 256;
 
 template <typename TH, typename TW>
 __global__ void __launch_bounds__(ROUTE_THREADS)
-moe_route_kernel(const TH* __restrict__ h, const TW* __restrict__ w_router, int T, int W, int E, int top, int renormalize,
-                 int softmax_scores, const float* __restrict__ correction, int groups, int keep, int num_real,
+moe_route_kernel(const TH* __restrict__ h, const TW* __restrict__ w_router, const float* __restrict__ bias, int T, int W, int E,
+                 int top, int renormalize, int softmax_scores, const float* __restrict__ correction, int groups, int keep, int num_real,
                  int* __restrict__ pair_expert, float* __restrict__ pair_weight, int* __restrict__ counts) {
     // A block takes ROUTE_TOK tokens: the router's rows are read once for all of them (2,048 tokens re-read a 64 KB router
     // 2,048 times otherwise), every token keeps sums of its own, and behind the products warp i does token i's choice.
@@ -99,7 +100,7 @@ moe_route_kernel(const TH* __restrict__ h, const TW* __restrict__ w_router, int 
         }
 #pragma unroll
         for (int k = 0; k < ROUTE_TOK; ++k) {
-            const float z = warp_sum(acc[k]);
+            const float z = warp_sum(acc[k]) + (bias ? bias[e] : 0.f);
             if (lane == 0) scores[(size_t)k * 3 * E + e] = softmax_scores ? z : 1.0f / (1.0f + expf(-z));
         }
     }
@@ -109,7 +110,7 @@ moe_route_kernel(const TH* __restrict__ h, const TW* __restrict__ w_router, int 
     float* score = scores + (size_t)warp * 3 * E;
     float* choice = score + E;
     float* gbest = choice + E;
-    if (softmax_scores) {                      // over all router outputs, in an order that E alone fixes
+    if (softmax_scores == 1) {                 // over all router outputs, in an order that E alone fixes
         float m = -INFINITY;
         for (int e = lane; e < E; e += 32) m = fmaxf(m, score[e]);
         m = warp_max(m);
@@ -174,6 +175,16 @@ moe_route_kernel(const TH* __restrict__ h, const TW* __restrict__ w_router, int 
         }
         total += wgt;
         __syncwarp();
+    }
+    if (softmax_scores == 2) {                 // the scores are the logits themselves: softmax over the chosen ones only
+        if (lane == 0) {
+            float* pw = pair_weight + (size_t)t * top;
+            float m = -INFINITY, sum = 0.f;
+            for (int k = 0; k < top; ++k) m = fmaxf(m, pw[k]);
+            for (int k = 0; k < top; ++k) { pw[k] = expf(pw[k] - m); sum += pw[k]; }
+            for (int k = 0; k < top; ++k) pw[k] /= sum;
+        }
+        return;
     }
     if (renormalize && lane == 0)
         for (int k = 0; k < top; ++k) pair_weight[(size_t)t * top + k] /= total;
@@ -260,10 +271,11 @@ moe_combine_kernel(const float* __restrict__ y, int W, int top, const float* __r
 }  // namespace
 
 // E router outputs, of which the last E - num_real are identity experts (pair_expert -1).  softmax_scores: the scores are
-// softmax(z) over all E outputs instead of sigmoid(z).  correction [E] float32 or null: added to the scores for the
+// softmax(z) over all E outputs instead of sigmoid(z); 2: the scores are the logits z, and the weights of the chosen are the
+// softmax over the chosen logits alone.  bias [E] float32 or null: added to the router's product.  correction [E] float32 or null: added to the scores for the
 // choice only.  groups > 1 with keep < groups: E / groups neighbours form a group, and only the ``keep`` groups whose best
 // choice score is largest can be chosen from.
-TFF_API int tff_moe_route(const void* h, int h_dt, const void* w_router, int w_dt, int T, int W, int E, int top,
+TFF_API int tff_moe_route(const void* h, int h_dt, const void* w_router, int w_dt, const float* bias, int T, int W, int E, int top,
                           int renormalize, int softmax_scores, const float* correction, int groups, int keep,
                           int num_real, int* pair_expert, float* pair_weight, int* counts, cudaStream_t stream) {
     if (T <= 0) return TFF_OK;
@@ -277,7 +289,7 @@ TFF_API int tff_moe_route(const void* h, int h_dt, const void* w_router, int w_d
         if (smem > 48 * 1024)                                                                                         \
             cudaFuncSetAttribute(moe_route_kernel<TH, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
         return tff_launch_pdl(moe_route_kernel<TH, TW>, dim3((T + ROUTE_TOK - 1) / ROUTE_TOK), dim3(ROUTE_THREADS), smem, stream, (const TH*)h, \
-                              (const TW*)w_router, T, W, E, top, renormalize, softmax_scores, correction, groups, keep, \
+                              (const TW*)w_router, bias, T, W, E, top, renormalize, softmax_scores, correction, groups, keep, \
                               num_real, pair_expert, pair_weight, counts);         \
     } while (0)
     if (h_dt == 0 && w_dt == 0) TFF_ROUTE(float, float);

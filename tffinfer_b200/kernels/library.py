@@ -525,14 +525,17 @@ class CudaKernels:
     # ------------------------------------------------------- mixers with a rotation computed on the fly
     def qkv_finish(self, proj, q_out, k_out, freq, batch, block_table, kv_cache, kv_layer, page_size, nq, nkv, d, dv,
                    k_scale: float = 1.0, v_mode: int = 0, v_share=None, lam=None, gate_off: int = -1, gate_out=None,
-                   last_reader: bool = True, proj_off: int = 0) -> None:
+                   last_reader: bool = True, proj_off: int = 0, bias=None, unit_eps: float = 0.0) -> None:
         """proj [T, ld] = [q (nq*d) | k (nkv*d) | v (nkv*dv) | ...] -> rotated q in ``q_out`` [T, nq*d]; rotated k
         (times ``k_scale``) and v into the tokens' cache slots or, with no cache, k into ``k_out`` (float32);
         ``freq`` = (frequencies, rot_dim, magnitude, interleaved) or None; value mixing and head gates as
         csrc/qkv_finish.cu describes them.  When ``proj`` is one of the accumulator buffers that are kept at zero
         between uses, what the kernel consumes is set back to zero; ``last_reader`` says that nothing of the row is
-        left for another kernel (which then clears the rest).  ``proj_off``: the row's q starts at that column."""
-        self._need_cuda(proj, q_out, k_out, block_table, v_share, lam, gate_out)
+        left for another kernel (which then clears the rest).  ``proj_off``: the row's q starts at that column.
+        ``bias``: float32 [nq*d + nkv*d + nkv*dv] added to q, k and v first; ``unit_eps`` > 0: every q and k head is
+        divided by sqrt(mean(x^2) + unit_eps) behind the rotation (an RMS norm without a weight)."""
+        self._need_cuda(proj, q_out, k_out, block_table, v_share, lam, gate_out, bias)
+        assert bias is None or (bias.dtype == torch.float32 and bias.numel() == nq * d + nkv * d + nkv * dv)
         T, ld = proj.shape
         f, rot, mag, inter = freq if freq is not None else (None, 0, 1.0, False)
         c_ptr, _, c_layers, c_layer = self._cache_args(kv_cache, kv_layer)
@@ -548,7 +551,8 @@ class CudaKernels:
             _c_int(block_table.shape[1] if block_table is not None else 0),
             c_ptr, _c_int(_dt(kv_cache)) if kv_cache is not None else _c_int(0), _c_int(c_layers), _c_int(c_layer),
             _c_int(page_size), _c_int(dc), _c_int(v_mode), _ptr(v_share), _ptr(lam), _c_int(gate_off), _ptr(gate_out),
-            _c_int(T), _c_int(nq), _c_int(nkv), _c_int(d), _c_int(dv), self._stream()), "qkv_finish")
+            _c_int(T), _c_int(nq), _c_int(nkv), _c_int(d), _c_int(dv), _ptr(bias), _c_float(unit_eps), self._stream()),
+            "qkv_finish")
         if clear and last_reader:
             self._acc_zero[proj.data_ptr()] = True
         self.launches += 1
@@ -699,12 +703,13 @@ class CudaKernels:
 
     def attention_tile(self, q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, dv, scale,
                        window: int = 0, chunk: int = 0, temp=None, r1=None, r2=None, out_scale: float = 1.0,
-                       out_off: int = 0, num_splits=None, dense=None) -> None:
+                       out_off: int = 0, num_splits=None, dense=None, softcap: float = 0.0) -> None:
         """q [T, nq*d] against the paged cache -> columns out_off .. out_off + nq*dv of ``out`` (times out_scale), in
         float32 arithmetic whatever the storage type.  The cache has two planes (keys, values) or one (the value
         of a token is the first dv elements of its key).  Visibility: causal, within ``window`` keys, within the
         query's block of ``chunk`` positions.  Scores: (q . k) * scale * temp[h] - r1[h] * ln(1 + r2[h] * distance)
-        (temp, r1, r2 float32 [nq] or None).  ``dense`` = (keys [T, nkv*d], values [T, nkv*dv]) of this step's own tokens
+        (temp, r1, r2 float32 [nq] or None); with ``softcap`` > 0 the scaled product is squashed to softcap * tanh(. / softcap)
+        ahead of the distance term.  ``dense`` = (keys [T, nkv*d], values [T, nkv*dv]) of this step's own tokens
         instead of the cache: for steps whose requests all start at position 0 (bfloat16, tensor-core form only)."""
         self._need_cuda(q, block_table, out, temp, r1, r2)
         T = q.shape[0]
@@ -733,7 +738,7 @@ class CudaKernels:
             _c_int(batch.max_q_len), _c_int(nq), _c_int(nkv), _c_int(d), _c_int(dv), _c_float(scale), _c_int(window),
             _c_int(chunk), _ptr(temp), _ptr(r1), _ptr(r2), _c_float(out_scale), _c_int(T), _c_int(splits), _ptr(part_o),
             _ptr(part_ml), _ptr(kd), _ptr(vd), _c_int(kd.shape[1] if kd is not None else 0),
-            _c_int(vd.shape[1] if vd is not None else 0), self._stream()), "attention_tile")
+            _c_int(vd.shape[1] if vd is not None else 0), _c_float(softcap), self._stream()), "attention_tile")
         self.launches += 2 if splits > 1 else 1
 
     def tile_splits(self, batch, nq: int, nkv: int, window: int = 0, chunk: int = 0) -> int:
@@ -1043,7 +1048,8 @@ class CudaKernels:
         ``padded_rows`` (a multiple of ``tile_rows``, at least T*top + E*(tile_rows-1)) every expert's rows start at a
         multiple of ``tile_rows``, x has that many rows, and two more are returned: lane_group (int32, the expert of
         every tile of x, -1 for tiles nobody uses) and place_of_pair (int32 [T*top]).  ``router`` = dict(score="sigmoid" |
-        "softmax", correction=float32 [outputs] or None, groups=(count, keep), identity=n): the router's last n outputs are
+        "softmax" | "softmax_chosen" (the logits choose, the chosen are weighted by a softmax among themselves),
+        bias=float32 [outputs] or None (added to the logits), correction=float32 [outputs] or None, groups=(count, keep), identity=n): the router's last n outputs are
         identity experts, whose pairs get no row (pair_expert -1; returned as a last, further value when n > 0)."""
         T, W = h.shape
         r = router or {}
@@ -1070,9 +1076,12 @@ class CudaKernels:
         lane_group = ints[o + 3 * max_tiles + 1:o + 3 * max_tiles + 1 + lane_tiles] if padded_rows else None
         place = ints[o + 3 * max_tiles + 1 + lane_tiles:] if padded_rows else None
         pair_weight = torch.empty(P, dtype=torch.float32, device=dev)
-        self._check(self.lib.tff_moe_route(_ptr(h), _c_int(_dt(h)), _ptr(w_router), _c_int(_dt(w_router)), _c_int(T), _c_int(W),
+        bias = r.get("bias")
+        self._need_cuda(bias)
+        assert bias is None or (bias.dtype == torch.float32 and bias.numel() == E + identity)
+        self._check(self.lib.tff_moe_route(_ptr(h), _c_int(_dt(h)), _ptr(w_router), _c_int(_dt(w_router)), _ptr(bias), _c_int(T), _c_int(W),
                                            _c_int(E + identity), _c_int(top), _c_int(1 if renormalize else 0),
-                                           _c_int(1 if r.get("score", "sigmoid") == "softmax" else 0), _ptr(correction),
+                                           _c_int({"sigmoid": 0, "softmax": 1, "softmax_chosen": 2}[r.get("score", "sigmoid")]), _ptr(correction),
                                            _c_int(int(groups)), _c_int(int(keep)), _c_int(E), _ptr(pair_expert),
                                            _ptr(pair_weight), _ptr(counts), self._stream()), "moe_route")
         self._check(self.lib.tff_moe_plan(_ptr(counts), _c_int(E), _c_int(bm), _ptr(cursor), _ptr(tile_group), _ptr(tile_row0),
@@ -1138,6 +1147,90 @@ class CudaKernels:
             self._acc_zero[proj.data_ptr()] = True
 
     GRU_CHUNKED_FROM = 32         # longest portion of a step from which the recurrence runs chunk by chunk
+
+    # ------------------------------------------------------- recurrences over a matrix state with a decay read from the input
+    def linear_recurrence(self, q, k, v, dec, state, batch, out, H: int, K: int, V: int, mode: str, share: int = 1,
+                          dec_bias=None, rate_log=None, skip=None, inv_tau: float = 1.0, q_scale: float = 1.0,
+                          state_off: int = 0) -> None:
+        """S_t = diag(a_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t (+ skip_h v_t) per head over a float32 state [K, V]
+        (csrc/linear_recurrence.cu).  q, k, v, dec are (float32 rows [T, ld], first column): column blocks of a
+        projection's accumulators or tensors of their own; ``share`` heads use one q and one k.  ``mode``: "log" (dec =
+        ln a per key channel), "gate" (a = sigmoid(dec + dec_bias)^inv_tau per key channel), "step" (dt = softplus(dec +
+        dec_bias) per head, a = exp(-exp(rate_log) dt), k times dt).  ``state`` [slots, n] float32: a request's heads lie
+        at elements state_off .. of its slot.  out float32 [T, H*V]."""
+        (qt, q0), (kt, k0), (vt, vo), (dt, d0) = q, k, v, dec
+        self._need_cuda(qt, kt, vt, dt, state, out, dec_bias, rate_log, skip)
+        for t in (qt, kt, vt, dt, state, out):
+            assert t.dtype == torch.float32
+        assert state.dim() == 2 and state_off + H * K * V <= state.shape[1] and tuple(out.shape) == (qt.shape[0], H * V)
+        G = H // share
+        assert H % share == 0 and q0 + G * K <= qt.shape[1] and k0 + G * K <= kt.shape[1] and vo + H * V <= vt.shape[1]
+        m = {"log": 0, "gate": 1, "step": 2}[mode]
+        assert d0 + (H if m == 2 else H * K) <= dt.shape[1]
+        for t, n in ((dec_bias, H if m == 2 else H * K), (rate_log, H), (skip, H)):
+            assert t is None or (t.dtype == torch.float32 and t.numel() == n)
+        self._check(self.lib.tff_linear_recurrence(
+            _ptr(qt), _c_int(qt.shape[1]), _c_int(q0), _ptr(kt), _c_int(kt.shape[1]), _c_int(k0), _ptr(vt),
+            _c_int(vt.shape[1]), _c_int(vo), _ptr(dt), _c_int(dt.shape[1]), _c_int(d0), _ptr(dec_bias), _ptr(rate_log),
+            _ptr(skip), _c_int(m), _c_float(inv_tau), _c_float(q_scale), _ptr(state), ctypes.c_longlong(state.shape[1]),
+            ctypes.c_longlong(state_off), _ptr(batch.q_start), _ptr(batch.pos_start), _ptr(batch.slots), _ptr(out),
+            _c_int(out.shape[1]), _c_int(batch.num_requests), _c_int(H), _c_int(K), _c_int(V), _c_int(share),
+            self._stream()), "linear_recurrence")
+        self.launches += 1
+
+    def gated_norm(self, o, group: int, gate, gate_off: int, weight, eps: float, gate_first: bool, out, out_off: int = 0,
+                   out_scale: float = 1.0, clear_cols=None, last_reader: bool = False) -> None:
+        """o float32 [T, width] in groups of ``group`` columns: RMS norm of every group times weight[c mod len(weight)]
+        and the silu of columns gate_off .. of the float32 rows ``gate``, the gate ahead of the norm (``gate_first``) or
+        behind it -> columns out_off .. of ``out`` times out_scale.  ``clear_cols`` = (lo, hi): when ``gate`` is one of
+        the accumulator buffers kept at zero between uses, those columns of it are set back to zero; ``last_reader``
+        says that nothing else of its rows is left unread, so that the buffer counts as clean again."""
+        self._need_cuda(o, gate, weight, out)
+        T, width = o.shape
+        assert o.dtype == gate.dtype == weight.dtype == torch.float32 and width % group == 0
+        assert gate_off + width <= gate.shape[1] and out.shape[0] == T and out_off + width <= out.shape[1]
+        clear = 1 if (clear_cols is not None and gate.data_ptr() in self._acc_zero) else 0
+        lo, hi = clear_cols if clear_cols is not None else (0, 0)
+        self._check(self.lib.tff_gated_norm(
+            _ptr(o), _c_int(width), _c_int(group), _ptr(gate), _c_int(gate.shape[1]), _c_int(gate_off), _ptr(weight),
+            _c_int(weight.numel()), _c_float(eps), _c_int(1 if gate_first else 0), _ptr(out), _c_int(_dt(out)),
+            _c_int(out.shape[1]), _c_int(out_off), _c_float(out_scale), _c_int(clear), _c_int(lo), _c_int(hi), _c_int(T),
+            self._stream()), "gated_norm")
+        if clear and last_reader:
+            self._acc_zero[gate.data_ptr()] = True
+        self.launches += 1
+
+    def causal_conv(self, proj, col0: int, channels: int, weight, bias, activation: str, state, state_off: int, batch,
+                    out) -> None:
+        """y[t, c] = act(bias[c] + sum_j weight[c, j] u[t - taps + 1 + j, c]) over columns col0 .. col0 + channels of the
+        float32 rows ``proj`` -> out float32 [T, channels]; the rows ahead of a request's portion come from elements
+        state_off .. of its slot of ``state`` [slots, n] ([taps-1, channels], oldest first), zeros ahead of position 0.
+        ``causal_conv_state`` behind it keeps the rows the next step needs."""
+        self._need_cuda(proj, weight, bias, state, out)
+        T = proj.shape[0]
+        taps = weight.shape[1]
+        assert proj.dtype == weight.dtype == out.dtype == torch.float32 and tuple(weight.shape) == (channels, taps)
+        assert tuple(out.shape) == (T, channels) and (bias is None or (bias.dtype == torch.float32 and bias.numel() == channels))
+        assert taps == 1 or (state is not None and state.dtype == torch.float32 and state.dim() == 2
+                             and state_off + (taps - 1) * channels <= state.shape[1])
+        self._check(self.lib.tff_causal_conv(
+            _ptr(proj), _c_int(proj.shape[1]), _c_int(col0), _c_int(channels), _ptr(weight), _ptr(bias), _c_int(taps),
+            _c_int({"none": 0, "silu": 1}[activation]), _ptr(state), ctypes.c_longlong(state.shape[1] if state is not None else 0),
+            ctypes.c_longlong(state_off), _ptr(batch.positions), _ptr(batch.tok_req), _ptr(batch.q_start), _ptr(batch.slots),
+            _ptr(out), _c_int(T), self._stream()), "causal_conv")
+        self.launches += 1
+
+    def causal_conv_state(self, proj, col0: int, channels: int, taps: int, state, state_off: int, batch) -> None:
+        """Every request's last taps-1 rows of columns col0 .. col0 + channels of ``proj`` go to its slot (older rows move
+        up when the portion is shorter)."""
+        if taps <= 1:
+            return
+        self._need_cuda(proj, state)
+        self._check(self.lib.tff_causal_conv_state(
+            _ptr(proj), _c_int(proj.shape[1]), _c_int(col0), _c_int(channels), _c_int(taps), _ptr(state),
+            ctypes.c_longlong(state.shape[1]), ctypes.c_longlong(state_off), _ptr(batch.q_start), _ptr(batch.slots),
+            _c_int(batch.num_requests), self._stream()), "causal_conv_state")
+        self.launches += 1
 
     # ------------------------------------------------------- latent attention
     PER_HEAD_FROM = 128       # longest portion of a step of whole prompts from which a latent attention makes per-head keys

@@ -230,19 +230,27 @@ class GatedSinkAttention(Mixer):
 
 @register_part("mixer", "biased_chunk_attention")
 class BiasedChunkAttention(SplitMixer):
-    """Grouped-query softmax attention without a rotation, whose scores carry the positions:
+    """Grouped-query softmax attention whose visibility is causal within blocks of ``chunk`` positions counted from
+    position 0 of the sequence (key n is seen from p only if n // chunk == p // chunk; 0 = no blocks) and/or within a
+    sliding ``window``, with, each a parameter:
 
-        score(p, n) = (q_p . k_n) * softmax_scale * temp_h  -  r1_h * ln(1 + r2_h * (p - n))
+    * scores that carry the positions, ``score(p, n) = (q_p . k_n) * softmax_scale * temp_h - r1_h * ln(1 + r2_h * (p - n))``
+      with learned per-head numbers temp (``head_temperature``) and r1, r2 (``distance_bias``);
+    * ``projection_bias``: biases of the q, k and v projections (tensors "<name>.b"), added in the projection;
+    * ``rotary``: part of every q and k head rotated by the layer's position encoding (``frequencies()``);
+    * ``unit_norm_eps`` > 0: every q and k head divided, behind the rotation, by sqrt(mean(x^2) + eps) (an RMS norm
+      without a weight);
+    * ``softcap`` > 0: the scaled product becomes softcap * tanh(. / softcap).
 
-    with learned per-head numbers temp (``head_temperature``) and r1, r2 (``distance_bias``), and whose visibility is
-    causal within blocks of ``chunk`` positions counted from position 0 of the sequence (key n is seen from p only if
-    n // chunk == p // chunk; 0 = no blocks) and/or within a sliding ``window``.  Keys of ``head_dim`` and values of
-    ``v_head_dim`` elements.  Everything behind the projections is float32 arithmetic (kernels/library.py
-    ``attention_tile``).  The cache keeps what a later query can still see: the last ``chunk`` (or ``window``) tokens."""
+    Keys of ``head_dim`` and values of ``v_head_dim`` elements.  Everything behind the projections is float32 arithmetic
+    (kernels/library.py ``attention_tile``).  The cache keeps what a later query can still see: the last ``chunk`` (or
+    ``window``) tokens."""
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, v_head_dim: int = 0,
                  softmax_scale: Optional[float] = None, chunk: int = 0, window: int = 0, head_temperature: bool = False,
-                 distance_bias: bool = False, names: Optional[Dict[str, str]] = None, prefix: str = ""):
+                 distance_bias: bool = False, projection_bias: bool = False, rotary: bool = False,
+                 unit_norm_eps: float = 0.0, softcap: float = 0.0, names: Optional[Dict[str, str]] = None,
+                 prefix: str = ""):
         super().__init__(prefix)
         self.hidden_size, self.num_heads, self.num_kv_heads = int(hidden_size), int(num_heads), int(num_kv_heads)
         self.head_dim = int(head_dim)
@@ -250,17 +258,20 @@ class BiasedChunkAttention(SplitMixer):
         self.scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(self.head_dim)
         self.chunk, self.window = int(chunk), int(window)
         self.head_temperature, self.distance_bias = bool(head_temperature), bool(distance_bias)
+        self.projection_bias, self.rotary = bool(projection_bias), bool(rotary)
+        self.unit_norm_eps, self.softcap = float(unit_norm_eps), float(softcap)
         if self.num_kv_heads <= 0 or self.num_heads % self.num_kv_heads:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
-        if self.chunk < 0 or self.window < 0:
-            raise ValueError("chunk and window must not be negative")
-        self.names = {"q": "q", "k": "k", "v": "v", "o": "o", "temp": "temp", "r1": "r1", "r2": "r2"}
+        if self.chunk < 0 or self.window < 0 or self.unit_norm_eps < 0 or self.softcap < 0:
+            raise ValueError("chunk, window, unit_norm_eps and softcap must not be negative")
+        self.names = {"q": "q", "k": "k", "v": "v", "o": "o", "temp": "temp", "r1": "r1", "r2": "r2", "q_bias": "q.b",
+                      "k_bias": "k.b", "v_bias": "v.b"}
         self.names.update(names or {})
         self.q_width = self.num_heads * self.head_dim
         self.k_width = self.num_kv_heads * self.head_dim
         self.v_width = self.num_kv_heads * self.v_head_dim
         self.cache_dim = max(self.head_dim, self.v_head_dim)     # a cache slot holds a key or a value
-        self.w_in = self.w_o = self.temp = self.r1 = self.r2 = None
+        self.w_in = self.w_o = self.temp = self.r1 = self.r2 = self.bias = None
 
     def cache_need(self):
         spans = [s for s in (self.chunk, self.window) if s > 0]
@@ -277,6 +288,9 @@ class BiasedChunkAttention(SplitMixer):
         if self.distance_bias:
             s[n["r1"]] = WeightSpec((self.num_heads,), VECTOR, init="one_plus_normal", init_scale=0.2)
             s[n["r2"]] = WeightSpec((self.num_heads,), VECTOR, init="one_plus_normal", init_scale=0.2)
+        if self.projection_bias:
+            for which, width in (("q_bias", self.q_width), ("k_bias", self.k_width), ("v_bias", self.v_width)):
+                s[n[which]] = WeightSpec((width,), VECTOR, init="normal", init_scale=0.3)
         return s
 
     def load(self, tensors, ops, act_dtype) -> None:
@@ -288,6 +302,8 @@ class BiasedChunkAttention(SplitMixer):
         self.temp = tensors[n["temp"]].contiguous() if self.head_temperature else None
         self.r1 = tensors[n["r1"]].contiguous() if self.distance_bias else None
         self.r2 = tensors[n["r2"]].contiguous() if self.distance_bias else None
+        if self.projection_bias:                     # one vector laid out like the projection's q | k | v columns
+            self.bias = torch.cat([tensors[n[w]].to(torch.float32) for w in ("q_bias", "k_bias", "v_bias")]).contiguous()
 
     def input_rows(self):
         return self.w_in
@@ -302,11 +318,18 @@ class BiasedChunkAttention(SplitMixer):
         if not ctx.write_cache:
             raise ValueError("biased_chunk_attention writes the keys and values it attends to; a borrowed cache is not supported")
         ops, batch = ctx.ops, ctx.batch
+        freq = None
+        if self.rotary:
+            freq = ctx.position.frequencies() if ctx.position is not None else None
+            if freq is None:
+                raise ValueError("biased_chunk_attention with rotary=True needs a position encoding that gives frequencies")
+            if freq[1] > self.head_dim:
+                raise ValueError(f"the rotation covers {freq[1]} dimensions, a head has {self.head_dim}")
         q = torch.empty((proj.shape[0], self.q_width), dtype=mixed.dtype, device=mixed.device)
-        ops.qkv_finish(proj, q, None, None, batch, ctx.block_table, ctx.kv_cache, ctx.kv_layer, ctx.page_size,
+        ops.qkv_finish(proj, q, None, freq, batch, ctx.block_table, ctx.kv_cache, ctx.kv_layer, ctx.page_size,
                        self.num_heads, self.num_kv_heads, self.head_dim, self.v_head_dim, last_reader=last_reader,
-                       proj_off=col)
+                       proj_off=col, bias=self.bias, unit_eps=self.unit_norm_eps)
         ops.attention_tile(q, batch, ctx.block_table, ctx.kv_cache, ctx.kv_layer, ctx.page_size, mixed, self.num_heads,
                            self.num_kv_heads, self.head_dim, self.v_head_dim, self.scale, window=self.window,
                            chunk=self.chunk, temp=self.temp, r1=self.r1, r2=self.r2, out_scale=out_scale,
-                           out_off=mixed_col)
+                           out_off=mixed_col, softcap=self.softcap)

@@ -20,7 +20,7 @@ INT_TABLE = "int"      # integer tables: held in int32
 
 @dataclass(frozen=True)
 class WeightSpec:
-    shape: Tuple[int, ...]
+    shape: Tuple[int, ...]                # a dimension of -1: whatever the file holds (random weights cannot be made then)
     role: str = MATRIX
     init: str = "normal"          # random-weights mode: "normal" | "one_plus_normal" | "eye_plus_normal" | "zeros"
     init_scale: Optional[float] = None   # std; None = the model's init_std (normal) or 0.1 (one_plus_normal)

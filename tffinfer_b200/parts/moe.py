@@ -1,8 +1,9 @@
 """Routed feed-forward (mixture of experts): ``num_experts`` small feed-forwards without biases, of which every
 token uses ``top``.
 
-    z = W_r h                                            router, computed in float32
-    s = sigmoid(z), or softmax(z) over all router outputs (``router_score``)
+    z = W_r h (+ b with ``router_bias``)                 router, computed in float32
+    s = sigmoid(z), or softmax(z) over all router outputs (``router_score``); "softmax_chosen": s = z chooses, and the
+        weights are the softmax over the chosen z alone
     c = s + correction                                   the choice scores (``correction``: a learned vector; else c = s)
     ``groups`` = (count, keep): the router outputs form ``count`` equal groups of neighbours, a group's score is its
         largest c, and only members of the ``keep`` best groups can be chosen
@@ -37,7 +38,7 @@ class RoutedExperts(FeedForward):
     def __init__(self, hidden_size: int, intermediate_size: int, num_experts: int, top: int, activation: str = "silu",
                  renormalize: bool = False, weight_on: str = "output", gated: bool = True, router_score: str = "sigmoid",
                  correction: bool = False, groups=None, identity_experts: int = 0, shared_intermediate: int = 0,
-                 names=None, prefix: str = ""):
+                 router_bias: bool = False, names=None, prefix: str = ""):
         super().__init__(prefix)
         self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
         self.num_experts, self.top = int(num_experts), int(top)
@@ -53,8 +54,9 @@ class RoutedExperts(FeedForward):
             raise ValueError(f"activation of {'gated' if self.gated else 'plain'} experts must be one of {allowed}, got '{activation}'")
         if weight_on not in ("input", "output"):
             raise ValueError(f"weight_on must be 'input' or 'output', got '{weight_on}'")
-        if router_score not in ("sigmoid", "softmax"):
-            raise ValueError(f"router_score must be 'sigmoid' or 'softmax', got '{router_score}'")
+        if router_score not in ("sigmoid", "softmax", "softmax_chosen"):
+            raise ValueError(f"router_score must be 'sigmoid', 'softmax' or 'softmax_chosen', got '{router_score}'")
+        self.router_bias = bool(router_bias)
         self.activation, self.renormalize, self.weight_on = activation, bool(renormalize), weight_on
         self.router_score, self.correction = router_score, bool(correction)
         count, keep = (int(v) for v in groups) if groups is not None else (1, 1)
@@ -63,10 +65,10 @@ class RoutedExperts(FeedForward):
                              f"leave at least top ({self.top}) of them")
         self.groups = (count, keep)
         self.shared_intermediate = int(shared_intermediate)
-        self.names = {"router": "router", "expert": "e{}", "gate": "gate", "up": "up", "down": "down",
+        self.names = {"router": "router", "router_bias": "router.b", "expert": "e{}", "gate": "gate", "up": "up", "down": "down",
                       "correction": "correction", "shared": "shared"}
         self.names.update(names or {})
-        self.w_router = self.w_gate_up = self.w_down = self.correction_w = None
+        self.w_router = self.w_gate_up = self.w_down = self.correction_w = self.router_bias_w = None
         self.shared_up = self.shared_down = None
         self.gate_up_layout = "blocked"
 
@@ -80,6 +82,8 @@ class RoutedExperts(FeedForward):
         s = {self.names["router"]: WeightSpec((self.outputs, self.hidden_size), MATRIX)}
         if self.correction:
             s[self.names["correction"]] = WeightSpec((self.outputs,), VECTOR, init="normal", init_scale=0.05)
+        if self.router_bias:
+            s[self.names["router_bias"]] = WeightSpec((self.outputs,), VECTOR, init="normal", init_scale=0.5)
         for e in range(self.num_experts):
             if self.gated:
                 s[self._expert(e, "gate")] = WeightSpec((self.intermediate_size, self.hidden_size), MATRIX)
@@ -100,6 +104,8 @@ class RoutedExperts(FeedForward):
         self.w_router = tensors[self.names["router"]]
         if self.correction:
             self.correction_w = tensors[self.names["correction"]].to(torch.float32).contiguous()
+        if self.router_bias:
+            self.router_bias_w = tensors[self.names["router_bias"]].to(torch.float32).contiguous()
         if self.gated:
             gates, ups = all_of("gate", "up")
             # one tensor for gate and up of all experts; the kernel library chooses how their rows are laid out
@@ -117,10 +123,11 @@ class RoutedExperts(FeedForward):
             self.shared_down = tensors[self._shared("down")]
 
     def _router(self):
-        if (self.router_score, self.correction_w, self.groups, self.identity_experts) == ("sigmoid", None, (1, 1), 0):
+        if (self.router_score, self.correction_w, self.groups, self.identity_experts, self.router_bias_w) == \
+                ("sigmoid", None, (1, 1), 0, None):
             return None
         return dict(score=self.router_score, correction=self.correction_w, groups=self.groups,
-                    identity=self.identity_experts)
+                    identity=self.identity_experts, bias=self.router_bias_w)
 
     def forward(self, h, ctx, residual):
         ops = ctx.ops

@@ -45,6 +45,12 @@ class WeightError(ValueError):
         super().__init__("\n".join(lines))
 
 
+def shape_fits(found, expected) -> bool:
+    """A dimension of -1 in ``expected`` takes whatever the file holds (a size that no configuration key gives)."""
+    found, expected = tuple(found), tuple(expected)
+    return len(found) == len(expected) and all(e == -1 or e == f for f, e in zip(found, expected))
+
+
 _FLOATS = (torch.float64, torch.float32, torch.float16, torch.bfloat16)
 _INTS = (torch.int64, torch.int32, torch.int16, torch.int8, torch.uint8)
 
@@ -76,7 +82,7 @@ def check_and_load(files: List[SafetensorsFile], expected: Dict[str, WeightSpec]
         if n not in where:
             continue
         dt, shape = where[n].info(n)
-        if tuple(shape) != tuple(spec.shape):
+        if not shape_fits(shape, spec.shape):
             wrong_shape.append((n, spec.shape, shape))
         if spec.role == INT_TABLE and dt not in _INTS:
             wrong_dtype.append((n, f"{dt} stored where an integer table is expected"))
@@ -109,7 +115,7 @@ def check_tensors(tensors: Dict[str, torch.Tensor], expected: Dict[str, WeightSp
     missing = sorted(n for n in expected if n not in tensors and not expected[n].optional)
     unexpected = sorted(n for n in tensors if n not in expected)
     wrong_shape = [(n, expected[n].shape, tuple(tensors[n].shape)) for n in expected
-                   if n in tensors and tuple(tensors[n].shape) != tuple(expected[n].shape)]
+                   if n in tensors and not shape_fits(tensors[n].shape, expected[n].shape)]
     wrong_dtype = []
     for n, spec in expected.items():
         if n in tensors:

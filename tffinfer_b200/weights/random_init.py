@@ -31,6 +31,9 @@ def _stream(seed: int, name: str) -> torch.Generator:
 def random_tensor(seed: int, name: str, spec: WeightSpec, init_std: float, norm_noise: float,
                   store_dtype: torch.dtype) -> torch.Tensor:
     g = _stream(seed, name)
+    if any(n < 0 for n in spec.shape):
+        raise ValueError(f"tensor '{name}' has a size that only a file gives ({list(spec.shape)}): the configuration must "
+                         f"state it where weights are made at random")
     if spec.role == INT_TABLE:
         return torch.zeros(spec.shape, dtype=torch.int32)
     if spec.init == "zeros":
