@@ -756,19 +756,124 @@ def run_sadupel(steps: int, warmup: int, sizes=None) -> int:
     return 0
 
 
+# The Nugosun design beside Dominex (the closest of the other models: layers listed one by one, a chunked attention
+# beside a recurrence with state slots, latent attention with borrowed vectors, routed experts) at the same width:
+# (width, latent heads, dim, rot_dim, vdim, q_rank, kv_rank, left heads, left kv heads, left dim, block, state-space heads,
+# head channels, state rows, gla heads, gla key size, gla value size, experts, chosen, expert ff, dense ff).  Eight layers:
+# parallel, latent, gla, gla, parallel, latent (reading layer 1's vectors), gla, latent; dense and routed feed-forwards
+# take turns.
+NUGOSUN_SIZES = {"2k": (2048, 16, 128, 64, 128, 768, 512, 16, 4, 128, 1024, 32, 64, 128, 8, 128, 256, 16, 2, 3072, 6144),
+                 "4k": (4096, 32, 128, 64, 128, 1536, 512, 32, 8, 128, 2048, 64, 64, 128, 16, 128, 256, 16, 2, 6144, 12288)}
+NUGOSUN_ORDER = ("parallel", "latent", "gla", "gla", "parallel", "latent", "gla", "latent")
+
+
+def nugosun_engine(size: str, max_live: int, cache_tokens: int, graphs: bool, step_tokens: int):
+    import torch
+    import tffinfer_b200 as tff
+    from tffinfer_b200.config.nugosun_config import (NugosunConfig, NugosunLayer, NugosunMlp, NugosunGla, NugosunAttention,
+                                                     NugosunStateSpace, NugosunLatent)
+    from tffinfer_b200.config.tipezen_config import RotaryConfig
+    from tffinfer_b200.weights import random_tensors_on_device
+    W, H, D, R, VD, QR, KR, LH, LG, LD, CH, SH, SP, SN, GH, GK, GV, E, TOP, F, DF = NUGOSUN_SIZES[size]
+    moe, dense = NugosunMlp("moe", F, E, TOP), NugosunMlp("dense", DF)
+    layers = []
+    for i, kind in enumerate(NUGOSUN_ORDER):
+        mlp = moe if i % 2 else dense
+        if kind == "parallel":
+            layers.append(NugosunLayer("parallel", left=NugosunAttention(
+                LH, LG, LD, LD, LD ** -0.5 * 4.0, 50.0, CH, RotaryConfig(2.5e5, LD // 2, (8.0, 1024.0, 32.0, 1.0))),
+                right=NugosunStateSpace(SH, SP, SN, 1, 4, 1), left_scale=0.8, right_scale=0.9, mlp=mlp))
+        elif kind == "latent":
+            layers.append(NugosunLayer("latent_attention", latent=NugosunLatent(
+                H, D, R, VD, QR, KR, (D + R) ** -0.5, RotaryConfig(5e5, R), 1 if i == 5 else None), mlp=mlp))
+        else:
+            layers.append(NugosunLayer("gla", gla=NugosunGla(GH, GK, GV, 16.0, 16), mlp=mlp))
+    cfg = NugosunConfig("Nugosun", vocab_size=TIPEZEN_VOCAB, hidden_size=W, embed_scale=W ** 0.5, norm_eps=1e-6,
+                        layers=tuple(layers))
+    tensors = random_tensors_on_device(cfg, 0, "cuda", "bfloat16")
+    ecfg = tff.EngineConfig(dtype="bfloat16", page_size=PAGE_SIZE, max_cache_tokens=cache_tokens, max_live_requests=max_live,
+                            max_tokens_per_step=step_tokens, max_model_len=8192, use_cuda_graphs=graphs)
+    runner = tff.ModelRunner(config=cfg, tensors=tensors, engine_config=ecfg)
+    del tensors
+    torch.cuda.empty_cache()
+    return tff.Engine(runner=runner), cfg
+
+
+def run_nugosun(steps: int, warmup: int, sizes=None) -> int:
+    """Prefill and decode throughput of the Nugosun design beside Dominex at the same layer sizes, one JSON line a point,
+    and for each model the device time of a step by kind of kernel call; for Nugosun also what its own kernels reach
+    as a fraction of the measured copy rate: the recurrence over the matrix states (the rows it reads and writes in a
+    prompt step, the states it reads and writes in a decode step), the convolution, the gated norm, the two norms in one
+    pass, and the rotation-and-cache-write kernel with biases and unit-norm heads."""
+    import torch
+    peaks = load_peaks()
+    steps = min(steps, 32)
+    P = PROMPT_LEN
+    clocks = ClockSampler()
+    clocks.start()
+    for size in (sizes or NUGOSUN_SIZES):
+        W, H, D, R, VD, QR, KR, LH, LG, LD, CH, SH, SP, SN, GH, GK, GV, E, TOP, F, DF = NUGOSUN_SIZES[size]
+        for model, make in (("nugosun", nugosun_engine), ("dominex", dominex_engine)):
+            need = 64 * (P + warmup + steps + 64 + 72)
+            engine, cfg = make(size, 64, need, True, P)
+            pms = prefill_run(engine, iters=3, warmup=2, seed=1, prompt_len=P)
+            print(json.dumps({"point": "prefill", "model": model, "size": size, "layers": TIPEZEN_LAYERS, "tokens": P,
+                              "ms": round(pms, 3), "tok_s": round(P / (pms / 1e3), 1)}), flush=True)
+            for b in (8, 64):
+                run = decode_run(engine, b, steps, warmup, seed=b, prompt_len=P)
+                print(json.dumps({"point": "decode", "model": model, "size": size, "layers": TIPEZEN_LAYERS, "batch": b,
+                                  "context": round(run["mean_context"]), "tok_s": round(run["tok_s"], 1),
+                                  "ms_per_step": round(run["ms_per_step"], 4), "launches_per_step": run["launches"] // steps}),
+                      flush=True)
+            del engine
+            torch.cuda.empty_cache()
+            engine, cfg = make(size, 8, 8 * (P + 64), False, P)
+            kinds = traced_kinds(engine, P, 8)
+            line = {"point": "kernels", "model": model, "size": size, "prefill_tokens": P, "decode_batch": 8,
+                    "prefill_ms_by_kind": kinds.get("prefill"), "decode_ms_by_kind": kinds.get("decode"), "peaks": peaks["source"]}
+            if model == "nugosun":
+                n_par, n_gla, n_lay = NUGOSUN_ORDER.count("parallel"), NUGOSUN_ORDER.count("gla"), len(NUGOSUN_ORDER)
+                inner, ch = SH * SP, SH * SP + 2 * SN
+                # the recurrence: float32 rows read (q, k, decay, v) and written (o) a token; a request's states read and written a step
+                rec_rows = lambda T: 4 * T * (n_gla * (3 * GH * GK + 2 * GH * GV) + n_par * (2 * SN + SH + 2 * inner))
+                rec_state = lambda B: 4 * 2 * B * (n_gla * GH * GK * GV + n_par * SH * SN * SP)
+                conv_b = lambda T: n_par * T * ch * 4 * 2
+                gnorm_b = lambda T: n_gla * T * GH * GV * (4 + 4 + 2) + n_par * T * inner * (4 + 4 + 2)
+                pair_b = lambda T: n_lay * T * W * (4 + 2 + 2)
+                finish_b = lambda T: n_par * T * ((LH + 2 * LG) * LD * 4 + LH * LD * 2 + 2 * LG * LD * 2)
+                fr = {}
+                for step, T, B in (("prefill", P, 1), ("decode", 8, 8)):
+                    k = kinds.get(step) or {}
+                    for kind, nbytes in (("linear_recurrence", rec_rows(T) + rec_state(B)), ("causal_conv", conv_b(T)),
+                                         ("gated_norm", gnorm_b(T)), ("rmsnorm_pair", pair_b(T)), ("qkv_finish", finish_b(T))):
+                        if kind in k:
+                            fr[f"{step}_{kind}_hbm_frac"] = round(nbytes / (k[kind][1] / 1e3) / 1e9 / peaks["hbm_gbs"], 4)
+                k = kinds.get("prefill") or {}
+                if "linear_recurrence" in k:      # multiply-adds of the recurrence: decay, outer product and read-out a state element
+                    flops = P * 6.0 * (n_gla * GH * GK * GV + n_par * SH * SN * SP)
+                    fr["prefill_linear_recurrence_fp32_tflops"] = round(flops / (k["linear_recurrence"][1] / 1e3) / 1e12, 2)
+                line["fractions"] = fr
+            print(json.dumps(line), flush=True)
+            del engine
+            torch.cuda.empty_cache()
+    clocks.stop()
+    print(json.dumps({"point": "clocks", "clocks": clocks.summary()}), flush=True)
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="headline", choices=["headline", "sweep", "attn_decode", "shapes", "tipezen", "dominex", "sadupel"] + sorted(WORKLOADS),
+    ap.add_argument("--workload", default="headline", choices=["headline", "sweep", "attn_decode", "shapes", "tipezen", "dominex", "sadupel", "nugosun"] + sorted(WORKLOADS),
                     help="headline: the decode/prefill benchmark; sweep: the same shape at further batch sizes and "
                          "context lengths; attn_decode: the decode attention alone; shapes: the layer sizes of the other "
-                         "models of the family; tipezen: the Tipezen design beside Qwen3 at equal layer sizes; dominex: the Dominex design beside Tipezen at equal layer sizes; sadupel: the Sadupel design beside Dominex at equal layer sizes; else a whole workload through "
+                         "models of the family; tipezen: the Tipezen design beside Qwen3 at equal layer sizes; dominex: the Dominex design beside Tipezen at equal layer sizes; sadupel: the Sadupel design beside Dominex at equal layer sizes; nugosun: the Nugosun design beside Dominex at equal layer sizes; else a whole workload through "
                          "the scheduler")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--size", default="", help="with --workload dominex or sadupel: one of its layer sizes (2k, 4k) instead of all")
+    ap.add_argument("--size", default="", help="with --workload dominex, sadupel or nugosun: one of its layer sizes (2k, 4k) instead of all")
     ap.add_argument("--layers", type=int, default=SHAPE["num_layers"],
                     help="fewer layers than the shape has (both numbers are reported)")
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (no batch 1 / 64, no prefill)")
@@ -797,6 +902,8 @@ def main() -> int:
         return run_dominex(args.steps, warmup, [args.size] if args.size else None)
     if args.workload == "sadupel":
         return run_sadupel(args.steps, warmup, [args.size] if args.size else None)
+    if args.workload == "nugosun":
+        return run_nugosun(args.steps, warmup, [args.size] if args.size else None)
     if args.workload != "headline":
         return run_workload(args.workload, 0 if args.layers == SHAPE["num_layers"] else args.layers)
 

@@ -213,15 +213,17 @@ def gated_ff(h, gate, up, down):
 
 
 def routed_ff(h, w, p: str, mlp: dict, margins: Optional[list] = None):
-    """Router logits W_r h + b; the ``top`` largest are chosen and weighted by the softmax over the chosen logits."""
+    """Router logits W_r h + b; the ``top`` largest are chosen and weighted by the softmax over the chosen logits.
+    ``margins`` collects one number a token: how close the choice was."""
     E, top = int(mlp["router"]["experts"]), int(mlp["router"]["top"])
     logits = h @ w[p + ".router"].T + w[p + ".router.b"]
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         order = sorted(range(E), key=lambda e: (-float(logits[t, e]), e))
         chosen = order[:top]
-        if margins is not None and top < E:
-            margins.append(float(logits[t, order[top - 1]] - logits[t, order[top]]))
+        if margins is not None:        # how far the last chosen logit is ahead of the best one left out, in units of the
+            spread = float(logits[t].std()) if E > 1 else 1.0          # token's logits' standard deviation
+            margins.append(float(logits[t, order[top - 1]] - logits[t, order[top]]) / max(spread, 1e-30) if top < E else float("inf"))
         wts = torch.softmax(logits[t, chosen], dim=0)
         for e, a in zip(chosen, wts):
             out[t] = out[t] + a * gated_ff(h[t:t + 1], w[f"{p}.e{e}.gate"], w[f"{p}.e{e}.up"], w[f"{p}.e{e}.down"])[0]
@@ -230,8 +232,11 @@ def routed_ff(h, w, p: str, mlp: dict, margins: Optional[list] = None):
 
 # ------------------------------------------------------------------------------------------------ the model
 def forward(config: dict, weights: Dict[str, torch.Tensor], tokens, dtype=torch.float64, layers_out: Optional[list] = None,
-            margins: Optional[list] = None):
-    """Logits [T, vocab] of a whole sequence.  ``layers_out`` collects the residual after every layer."""
+            margins: Optional[list] = None, round_inputs: bool = False):
+    """Logits [T, vocab] of a whole sequence.  ``layers_out`` collects the residual after every layer.  With
+    ``round_inputs`` every norm's output is rounded to bfloat16, as an engine that computes in 16 bits rounds the
+    inputs of its products: how far that alone moves a position says how well conditioned the position is."""
+    r16 = (lambda t: t.to(torch.bfloat16).to(dtype)) if round_inputs else (lambda t: t)
     w = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in weights.items()}
     eps = float(config["norm"]["eps"])
     tokens = torch.as_tensor(tokens, dtype=torch.long)
@@ -240,7 +245,7 @@ def forward(config: dict, weights: Dict[str, torch.Tensor], tokens, dtype=torch.
     latents = {}
     for i, layer in enumerate(config["layers"]):
         p, m = f"l{i}", layer["mixer"]
-        h = rms_norm(x, w[p + ".norm1"], eps, True)
+        h = r16(rms_norm(x, w[p + ".norm1"], eps, True))
         if layer["type"] == "gla":
             y = gla_mixer(h, w, p + ".mix", dict(m, eps=eps))
         elif layer["type"] == "parallel":
@@ -257,7 +262,7 @@ def forward(config: dict, weights: Dict[str, torch.Tensor], tokens, dtype=torch.
             raise ValueError(layer["type"])
         mlp = layer.get("mlp")
         if mlp is not None:
-            h2 = rms_norm(x, w[p + ".norm2"], eps, True)
+            h2 = r16(rms_norm(x, w[p + ".norm2"], eps, True))
             if mlp["kind"] == "dense":
                 y = y + gated_ff(h2, w[p + ".mlp.gate"], w[p + ".mlp.up"], w[p + ".mlp.down"])
             else:
@@ -265,7 +270,7 @@ def forward(config: dict, weights: Dict[str, torch.Tensor], tokens, dtype=torch.
         x = x + y
         if layers_out is not None:
             layers_out.append(x.clone())
-    return rms_norm(x, w["final.norm"], eps, True) @ w["embed"].T
+    return r16(rms_norm(x, w["final.norm"], eps, True)) @ w["embed"].T
 
 
 def greedy(config: dict, weights, prompt, new_tokens: int, dtype=torch.float64):

@@ -7,7 +7,9 @@
 // request's first token of the step come from its slot: state + slot * slot_stride + state_off holds [taps-1, C]
 // float32, the oldest row first.  A tap that reaches back beyond position 0 reads zero, whatever the slot holds.
 // The second kernel, launched behind the first, leaves a request's last taps-1 rows of u in its slot (older rows move
-// up when the portion is shorter than that).  act: 0 none, 1 silu.
+// up when the portion is shorter than that).  In a step in which every request brings one token the first kernel does
+// that itself (``update_state``): the thread of a channel has read all of the channel's rows before it writes them.
+// act: 0 none, 1 silu.
 #include "common.cuh"
 
 namespace {
@@ -16,17 +18,17 @@ constexpr int CONV_MAX_TAPS = 16;
 
 __global__ void __launch_bounds__(256)
 causal_conv_kernel(const float* __restrict__ proj, int ld, int col0, int C, const float* __restrict__ w,
-                   const float* __restrict__ bias, int taps, int act, const float* __restrict__ state,
+                   const float* __restrict__ bias, int taps, int act, float* __restrict__ state,
                    long long slot_stride, long long state_off, const int* __restrict__ positions,
                    const int* __restrict__ tok_req, const int* __restrict__ q_start, const int* __restrict__ slots,
-                   float* __restrict__ out) {
+                   float* __restrict__ out, int update_state) {
     pdl_launch_dependents();
     const int t = blockIdx.x;
     const int c = blockIdx.y * 256 + threadIdx.x;
     if (c >= C) return;
     const int b = tok_req[t], pos = positions[t];
     const int i_in = t - q_start[b];                        // the token's place in its request's portion
-    const float* st = state ? state + (size_t)slots[b] * slot_stride + state_off : nullptr;
+    float* st = state ? state + (size_t)slots[b] * slot_stride + state_off : nullptr;
     float wc[CONV_MAX_TAPS];
     for (int j = 0; j < taps; ++j) wc[j] = w[(size_t)c * taps + j];
     float y = bias ? bias[c] : 0.f;
@@ -40,6 +42,10 @@ causal_conv_kernel(const float* __restrict__ proj, int ld, int col0, int C, cons
     }
     if (act == 1) y = y / (1.f + expf(-y));
     out[(size_t)t * C + c] = y;
+    if (update_state && taps > 1) {                         // the request's one token: its rows move up by one
+        for (int i = 0; i + 2 < taps; ++i) st[(size_t)i * C + c] = st[(size_t)(i + 1) * C + c];
+        st[(size_t)(taps - 2) * C + c] = proj[(size_t)t * ld + col0 + c];
+    }
 }
 
 __global__ void __launch_bounds__(256)
@@ -64,15 +70,15 @@ causal_conv_state_kernel(const float* __restrict__ proj, int ld, int col0, int C
 }  // namespace
 
 TFF_API int tff_causal_conv(const float* proj, int ld, int col0, int C, const float* w, const float* bias, int taps,
-                            int act, const float* state, long long slot_stride, long long state_off,
+                            int act, float* state, long long slot_stride, long long state_off,
                             const int* positions, const int* tok_req, const int* q_start, const int* slots, float* out,
-                            int num_tokens, cudaStream_t stream) {
+                            int num_tokens, int update_state, cudaStream_t stream) {
     if (num_tokens <= 0) return TFF_OK;
     if (!proj || !w || !out || C <= 0 || col0 < 0 || col0 + C > ld || taps < 1 || taps > CONV_MAX_TAPS ||
         (taps > 1 && !state) || act < 0 || act > 1)
         return TFF_ERR_BAD_ARGUMENT;
     return tff_launch_pdl(causal_conv_kernel, dim3(num_tokens, (C + 255) / 256), dim3(256), 0, stream, proj, ld, col0, C, w,
-                          bias, taps, act, state, slot_stride, state_off, positions, tok_req, q_start, slots, out);
+                          bias, taps, act, state, slot_stride, state_off, positions, tok_req, q_start, slots, out, update_state);
 }
 
 TFF_API int tff_causal_conv_state(const float* proj, int ld, int col0, int C, int taps, float* state, long long slot_stride,

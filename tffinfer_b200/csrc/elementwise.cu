@@ -132,6 +132,84 @@ TFF_API int tff_rmsnorm(const float* x, const float* w, const int* row_index, vo
     return tff_launch_pdl(rmsnorm_kernel<float, 64>, rows, 64, 0, stream, x, w, row_index, (float*)out, dim, eps);
 }
 
+// Two RMSNorms of the same rows with weights of their own (a layer whose two sublayers each norm the same residual):
+// out_a = (x * r) * w_a, out_b = (x * r) * w_b with the one r = rsqrt(mean(x^2) + eps).  The row is read once; the sum of
+// squares is added in the order rmsnorm_kernel uses for a row of this width, so either output equals that kernel's.
+template <typename TO, int NT>
+__global__ void rmsnorm_pair_kernel(const float* __restrict__ x, const float* __restrict__ wa, const float* __restrict__ wb,
+                                    TO* __restrict__ out_a, TO* __restrict__ out_b, int dim, float eps) {
+    __shared__ float red[32];
+    pdl_launch_dependents();
+    const int r = blockIdx.x;
+    const float* xr = x + (size_t)r * dim;
+    TO* oa = out_a + (size_t)r * dim;
+    TO* ob = out_b + (size_t)r * dim;
+    float ss = 0.f;
+    const bool vec = (dim & 3) == 0 && (((uintptr_t)xr | (uintptr_t)wa | (uintptr_t)wb) & 15) == 0 &&
+                     (((uintptr_t)oa | (uintptr_t)ob) & 7) == 0 &&
+                     (sizeof(TO) == 2 || (((uintptr_t)oa | (uintptr_t)ob) & 15) == 0);
+    pdl_wait();
+    if (vec) {
+        const float4* x4 = reinterpret_cast<const float4*>(xr);
+        const float4* a4 = reinterpret_cast<const float4*>(wa);
+        const float4* b4 = reinterpret_cast<const float4*>(wb);
+        const int n4 = dim >> 2;
+        constexpr int KEEP = 4;
+        float4 keep[KEEP];
+#pragma unroll
+        for (int k = 0; k < KEEP; ++k) {
+            const int i = threadIdx.x + k * NT;
+            keep[k] = i < n4 ? x4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int k = 0; k < KEEP; ++k) {
+            ss = fmaf(keep[k].x, keep[k].x, ss); ss = fmaf(keep[k].y, keep[k].y, ss);
+            ss = fmaf(keep[k].z, keep[k].z, ss); ss = fmaf(keep[k].w, keep[k].w, ss);
+        }
+        for (int i = threadIdx.x + KEEP * NT; i < n4; i += NT) {
+            const float4 v = x4[i];
+            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+        }
+        ss = block_sum<NT>(ss, red);
+        const float rs = rsqrtf(ss / (float)dim + eps);
+#pragma unroll
+        for (int k = 0; k < KEEP; ++k) {
+            const int i = threadIdx.x + k * NT;
+            if (i < n4) {
+                const float4 v = keep[k], ga = a4[i], gb = b4[i];
+                store4<TO>(oa + 4 * i, (v.x * rs) * ga.x, (v.y * rs) * ga.y, (v.z * rs) * ga.z, (v.w * rs) * ga.w);
+                store4<TO>(ob + 4 * i, (v.x * rs) * gb.x, (v.y * rs) * gb.y, (v.z * rs) * gb.z, (v.w * rs) * gb.w);
+            }
+        }
+        for (int i = threadIdx.x + KEEP * NT; i < n4; i += NT) {
+            const float4 v = x4[i], ga = a4[i], gb = b4[i];
+            store4<TO>(oa + 4 * i, (v.x * rs) * ga.x, (v.y * rs) * ga.y, (v.z * rs) * ga.z, (v.w * rs) * ga.w);
+            store4<TO>(ob + 4 * i, (v.x * rs) * gb.x, (v.y * rs) * gb.y, (v.z * rs) * gb.z, (v.w * rs) * gb.w);
+        }
+        return;
+    }
+    for (int i = threadIdx.x; i < dim; i += NT) { const float v = xr[i]; ss = fmaf(v, v, ss); }
+    ss = block_sum<NT>(ss, red);
+    const float rs = rsqrtf(ss / (float)dim + eps);
+    for (int i = threadIdx.x; i < dim; i += NT) {
+        const float v = xr[i] * rs;
+        oa[i] = from_f32<TO>(v * wa[i]);
+        ob[i] = from_f32<TO>(v * wb[i]);
+    }
+}
+
+TFF_API int tff_rmsnorm_pair(const float* x, const float* wa, const float* wb, void* out_a, void* out_b, int out_is_bf16,
+                             int rows, int dim, float eps, cudaStream_t stream) {
+    if (rows <= 0) return TFF_OK;
+    if (dim <= 0 || !x || !wa || !wb || !out_a || !out_b) return TFF_ERR_BAD_ARGUMENT;
+    if (dim >= 1024) {
+        if (out_is_bf16) return tff_launch_pdl(rmsnorm_pair_kernel<bf16, 256>, rows, 256, 0, stream, x, wa, wb, (bf16*)out_a, (bf16*)out_b, dim, eps);
+        return tff_launch_pdl(rmsnorm_pair_kernel<float, 256>, rows, 256, 0, stream, x, wa, wb, (float*)out_a, (float*)out_b, dim, eps);
+    }
+    if (out_is_bf16) return tff_launch_pdl(rmsnorm_pair_kernel<bf16, 64>, rows, 64, 0, stream, x, wa, wb, (bf16*)out_a, (bf16*)out_b, dim, eps);
+    return tff_launch_pdl(rmsnorm_pair_kernel<float, 64>, rows, 64, 0, stream, x, wa, wb, (float*)out_a, (float*)out_b, dim, eps);
+}
+
 // ------------------------------------------------------------------- SwiGLU
 // out[t, i] = silu(gu[t, i]) * gu[t, I + i], silu(g) = g / (1 + exp(-g))
 // (src/kernel/cuda/unary.cu:10-27: x1 = gate, x2 = up).

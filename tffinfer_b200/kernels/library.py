@@ -189,6 +189,18 @@ class CudaKernels:
                                          _c_int(rows), _c_int(dim), _c_float(eps), self._stream()), "rmsnorm")
         self.launches += 1
 
+    def rmsnorm_pair(self, x, weight_a, weight_b, eps: float, out_a, out_b) -> None:
+        """Two RMS norms of the same float32 rows with a weight each, the rows read once (a layer whose two sublayers
+        each norm the same residual)."""
+        self._need_cuda(x, weight_a, weight_b, out_a, out_b)
+        rows, dim = x.shape
+        assert x.dtype == weight_a.dtype == weight_b.dtype == torch.float32 and weight_a.numel() == weight_b.numel() == dim
+        assert out_a.dtype == out_b.dtype and tuple(out_a.shape) == tuple(out_b.shape) == (rows, dim)
+        self._check(self.lib.tff_rmsnorm_pair(_ptr(x), _ptr(weight_a), _ptr(weight_b), _ptr(out_a), _ptr(out_b),
+                                              _c_int(_dt(out_a)), _c_int(rows), _c_int(dim), _c_float(eps), self._stream()),
+                    "rmsnorm_pair")
+        self.launches += 1
+
     def gemm(self, a, w, out, residual=None) -> None:
         """out[M, N] = a[M, K] @ w[N, K]^T (+ residual, float32 [M, N]; may be ``out``)."""
         self._need_cuda(a, w, out, residual)
@@ -1201,11 +1213,12 @@ class CudaKernels:
         self.launches += 1
 
     def causal_conv(self, proj, col0: int, channels: int, weight, bias, activation: str, state, state_off: int, batch,
-                    out) -> None:
+                    out, update_state: bool = False) -> bool:
         """y[t, c] = act(bias[c] + sum_j weight[c, j] u[t - taps + 1 + j, c]) over columns col0 .. col0 + channels of the
         float32 rows ``proj`` -> out float32 [T, channels]; the rows ahead of a request's portion come from elements
         state_off .. of its slot of ``state`` [slots, n] ([taps-1, channels], oldest first), zeros ahead of position 0.
-        ``causal_conv_state`` behind it keeps the rows the next step needs."""
+        ``causal_conv_state`` behind it keeps the rows the next step needs; in a step in which every request brings one
+        token ``update_state`` lets this kernel do that itself; returns whether it did."""
         self._need_cuda(proj, weight, bias, state, out)
         T = proj.shape[0]
         taps = weight.shape[1]
@@ -1213,12 +1226,14 @@ class CudaKernels:
         assert tuple(out.shape) == (T, channels) and (bias is None or (bias.dtype == torch.float32 and bias.numel() == channels))
         assert taps == 1 or (state is not None and state.dtype == torch.float32 and state.dim() == 2
                              and state_off + (taps - 1) * channels <= state.shape[1])
+        fused = bool(update_state) and batch.max_q_len == 1 and taps > 1
         self._check(self.lib.tff_causal_conv(
             _ptr(proj), _c_int(proj.shape[1]), _c_int(col0), _c_int(channels), _ptr(weight), _ptr(bias), _c_int(taps),
             _c_int({"none": 0, "silu": 1}[activation]), _ptr(state), ctypes.c_longlong(state.shape[1] if state is not None else 0),
             ctypes.c_longlong(state_off), _ptr(batch.positions), _ptr(batch.tok_req), _ptr(batch.q_start), _ptr(batch.slots),
-            _ptr(out), _c_int(T), self._stream()), "causal_conv")
+            _ptr(out), _c_int(T), _c_int(1 if fused else 0), self._stream()), "causal_conv")
         self.launches += 1
+        return fused
 
     def causal_conv_state(self, proj, col0: int, channels: int, taps: int, state, state_off: int, batch) -> None:
         """Every request's last taps-1 rows of columns col0 .. col0 + channels of ``proj`` go to its slot (older rows move

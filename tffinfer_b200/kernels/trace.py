@@ -30,7 +30,7 @@ TRACED = ("embed", "rmsnorm", "gemm", "gemm_simt", "gemm_tc", "zero_f32", "gathe
           "qkv_project", "qk_norm_rope_kv_write", "attention", "attention_bf16", "attention_generic", "argmax",
           "sample", "repetition_penalty", "reset_state_slots", "logit_transform", "rope_table", "stream_step",
           "qkv_finish", "attend_gated", "attention_ext", "retain", "retention", "gated_act", "gemm_gated_act",
-          "gated_mlp", "attention_tile", "gemm_grouped", "routed_mlp", "moe_dispatch", "moe_combine", "min_gru",
+          "gated_mlp", "attention_tile", "gemm_grouped", "routed_mlp", "moe_dispatch", "moe_combine", "min_gru", "linear_recurrence", "gated_norm", "causal_conv", "causal_conv_state", "rmsnorm_pair",
           "latent_attend", "latent_finish", "latent_q_rot", "gemm_tc_grouped", "short_conv_norm", "short_conv_state",
           "pair_embed", "unary_act", "plain_mlp", "gemm_act", "conv_finish")
 

@@ -90,8 +90,9 @@ class SelectiveStateSpace(SplitMixer):
         T = proj.shape[0]
         H, P, N = self.num_heads, self.head_dim, self.state_size
         xbc = torch.empty((T, self.channels), dtype=torch.float32, device=proj.device)
-        ops.causal_conv(proj, col + self.inner, self.channels, self.conv_w, self.conv_b, "silu", ctx.state, 0, batch, xbc)
-        ops.causal_conv_state(proj, col + self.inner, self.channels, self.conv_taps, ctx.state, 0, batch)
+        if not ops.causal_conv(proj, col + self.inner, self.channels, self.conv_w, self.conv_b, "silu", ctx.state, 0, batch,
+                               xbc, update_state=True):          # single tokens: the rows move up in the same kernel
+            ops.causal_conv_state(proj, col + self.inner, self.channels, self.conv_taps, ctx.state, 0, batch)
         y = torch.empty((T, self.inner), dtype=torch.float32, device=proj.device)
         ops.linear_recurrence((xbc, self.inner + self.bc), (xbc, self.inner), (xbc, 0),
                               (proj, col + 2 * self.inner + 2 * self.bc), ctx.state, batch, y, H, N, P, "step",
