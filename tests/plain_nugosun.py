@@ -21,6 +21,17 @@ import torch
 
 
 # ------------------------------------------------------------------------------------------------ small pieces
+_ROUND = [None]     # set by forward(round_inputs=True): what an engine that computes in 16 bits rounds ahead of a product
+
+
+def lin(x, w, b=None):
+    """W x (+ b) for rows x; the rows are rounded first when forward() asks for it."""
+    if _ROUND[0] is not None:
+        x = _ROUND[0](x)
+    y = x @ w.T
+    return y if b is None else y + b
+
+
 def rms_norm(x, w, eps: float, unit_offset: bool = False):
     """x / sqrt(mean(x^2) + eps) times (1 + w) or w; no weight when w is None."""
     y = x / torch.sqrt((x * x).mean(dim=-1, keepdim=True) + eps)
@@ -106,10 +117,10 @@ def gla_mixer(h, w: Dict[str, torch.Tensor], p: str, m: dict, states: Optional[l
     """Gated linear attention with a decay per key channel read from the input through a low-rank pair of matrices."""
     T = h.shape[0]
     H, K, V, tau = int(m["heads"]), int(m["dim"]), int(m["vdim"]), float(m["tau"])
-    q = (h @ w[p + ".q"].T).reshape(T, H, K) * K ** -0.5
-    k = (h @ w[p + ".k"].T).reshape(T, H, K)
-    v = (h @ w[p + ".v"].T).reshape(T, H, V)
-    z = ((h @ w[p + ".a1"].T) @ w[p + ".a2"].T + w[p + ".a2.b"]).reshape(T, H, K)
+    q = lin(h, w[p + ".q"]).reshape(T, H, K) * K ** -0.5
+    k = lin(h, w[p + ".k"]).reshape(T, H, K)
+    v = lin(h, w[p + ".v"]).reshape(T, H, V)
+    z = lin(lin(h, w[p + ".a1"]), w[p + ".a2"], w[p + ".a2.b"]).reshape(T, H, K)
     log_alpha = torch.nn.functional.logsigmoid(z) / tau
     outs = []
     for hd in range(H):
@@ -117,7 +128,7 @@ def gla_mixer(h, w: Dict[str, torch.Tensor], p: str, m: dict, states: Optional[l
         if states is not None:
             states.append(S)
         outs.append(rms_norm(o, w[p + ".norm"], float(m["eps"])))
-    return (torch.cat(outs, dim=-1) * silu(h @ w[p + ".g"].T)) @ w[p + ".o"].T
+    return lin(torch.cat(outs, dim=-1) * silu(lin(h, w[p + ".g"])), w[p + ".o"])
 
 
 def chunked_attention(h, positions, w, p: str, m: dict, eps: float):
@@ -126,9 +137,9 @@ def chunked_attention(h, positions, w, p: str, m: dict, eps: float):
     block of mask.size positions counted from position 0."""
     T = h.shape[0]
     H, G, D, V = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
-    q = (h @ w[p + ".q"].T + w[p + ".q.b"]).reshape(T, H, D)
-    k = (h @ w[p + ".k"].T + w[p + ".k.b"]).reshape(T, G, D)
-    v = (h @ w[p + ".v"].T + w[p + ".v.b"]).reshape(T, G, V)
+    q = lin(h, w[p + ".q"], w[p + ".q.b"]).reshape(T, H, D)
+    k = lin(h, w[p + ".k"], w[p + ".k.b"]).reshape(T, G, D)
+    v = lin(h, w[p + ".v"], w[p + ".v.b"]).reshape(T, G, V)
     if m.get("rot"):
         q, k = rotate(q, positions, m["rot"], False), rotate(k, positions, m["rot"], False)
     q, k = rms_norm(q, None, eps), rms_norm(k, None, eps)
@@ -144,7 +155,7 @@ def chunked_attention(h, positions, w, p: str, m: dict, eps: float):
         if cap > 0:
             s = cap * torch.tanh(s / cap)
         outs.append(softmax_rows(s, visible) @ v[:, g])
-    return torch.cat(outs, dim=-1) @ w[p + ".o"].T
+    return lin(torch.cat(outs, dim=-1), w[p + ".o"])
 
 
 def causal_conv(u, weight, bias):
@@ -163,7 +174,7 @@ def ssd_mixer(h, w, p: str, m: dict, eps: float, states: Optional[list] = None):
     T = h.shape[0]
     H, V, N, G = int(m["heads"]), int(m["vdim"]), int(m["state"]), int(m["groups"])
     inner = H * V
-    proj = h @ w[p + ".in"].T
+    proj = lin(h, w[p + ".in"])
     z, xbc, dt = proj[:, :inner], proj[:, inner:2 * inner + 2 * G * N], proj[:, 2 * inner + 2 * G * N:]
     xbc = silu(causal_conv(xbc, w[p + ".conv"], w[p + ".conv.b"]))
     x = xbc[:, :inner].reshape(T, H, V)
@@ -182,41 +193,41 @@ def ssd_mixer(h, w, p: str, m: dict, eps: float, states: Optional[list] = None):
     y = torch.cat(ys, dim=-1) * silu(z)
     parts = int(m["norm_groups"])
     y = rms_norm(y.reshape(T, parts, inner // parts), None, eps).reshape(T, inner) * w[p + ".norm"]
-    return y @ w[p + ".o"].T
+    return lin(y, w[p + ".o"])
 
 
 def latent_of(h, positions, w, p: str, m: dict, eps: float):
     """What a latent layer caches: (c [T, kv_rank] normed, r [T, rot_dim] rotated)."""
     kv_rank = int(m["kv_rank"])
-    d = h @ w[p + ".dkv"].T
+    d = lin(h, w[p + ".dkv"])
     return rms_norm(d[:, :kv_rank], w[p + ".dkv.norm"], eps), rotate(d[:, kv_rank:], positions, m["rot"], True)
 
 
 def latent_attention(h, positions, c, r, w, p: str, m: dict, eps: float):
     T = h.shape[0]
     H, D, R, V = int(m["heads"]), int(m["dim"]), int(m["rot_dim"]), int(m["vdim"])
-    q = (rms_norm(h @ w[p + ".dq"].T, w[p + ".dq.norm"], eps) @ w[p + ".uq"].T).reshape(T, H, D + R)
+    q = lin(rms_norm(lin(h, w[p + ".dq"]), w[p + ".dq.norm"], eps), w[p + ".uq"]).reshape(T, H, D + R)
     q_rot = rotate(q[..., D:], positions, m["rot"], True)
-    keys = (c @ w[p + ".uk"].T).reshape(T, H, D)
-    vals = (c @ w[p + ".uv"].T).reshape(T, H, V)
+    keys = lin(c, w[p + ".uk"]).reshape(T, H, D)
+    vals = lin(c, w[p + ".uv"]).reshape(T, H, V)
     visible = positions[None, :] <= positions[:, None]
     outs = []
     for hd in range(H):
         s = (q[:, hd, :D] @ keys[:, hd].T + q_rot[:, hd] @ r.T) * float(m["scale"])
         outs.append(softmax_rows(s, visible) @ vals[:, hd])
-    return torch.cat(outs, dim=-1) @ w[p + ".o"].T
+    return lin(torch.cat(outs, dim=-1), w[p + ".o"])
 
 
 # ------------------------------------------------------------------------------------------------ feed-forwards
 def gated_ff(h, gate, up, down):
-    return (silu(h @ gate.T) * (h @ up.T)) @ down.T
+    return lin(silu(lin(h, gate)) * lin(h, up), down)
 
 
 def routed_ff(h, w, p: str, mlp: dict, margins: Optional[list] = None):
     """Router logits W_r h + b; the ``top`` largest are chosen and weighted by the softmax over the chosen logits.
     ``margins`` collects one number a token: how close the choice was."""
     E, top = int(mlp["router"]["experts"]), int(mlp["router"]["top"])
-    logits = h @ w[p + ".router"].T + w[p + ".router.b"]
+    logits = lin(h, w[p + ".router"], w[p + ".router.b"])
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         order = sorted(range(E), key=lambda e: (-float(logits[t, e]), e))
@@ -234,9 +245,16 @@ def routed_ff(h, w, p: str, mlp: dict, margins: Optional[list] = None):
 def forward(config: dict, weights: Dict[str, torch.Tensor], tokens, dtype=torch.float64, layers_out: Optional[list] = None,
             margins: Optional[list] = None, round_inputs: bool = False):
     """Logits [T, vocab] of a whole sequence.  ``layers_out`` collects the residual after every layer.  With
-    ``round_inputs`` every norm's output is rounded to bfloat16, as an engine that computes in 16 bits rounds the
-    inputs of its products: how far that alone moves a position says how well conditioned the position is."""
-    r16 = (lambda t: t.to(torch.bfloat16).to(dtype)) if round_inputs else (lambda t: t)
+    ``round_inputs`` the rows that enter a product with a weight matrix are rounded to bfloat16 first, as an engine that
+    computes in 16 bits rounds them: how far that alone moves a position says how well conditioned the position is."""
+    _ROUND[0] = (lambda t: t.to(torch.bfloat16).to(t.dtype)) if round_inputs else None
+    try:
+        return _forward(config, weights, tokens, dtype, layers_out, margins)
+    finally:
+        _ROUND[0] = None
+
+
+def _forward(config, weights, tokens, dtype, layers_out, margins):
     w = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in weights.items()}
     eps = float(config["norm"]["eps"])
     tokens = torch.as_tensor(tokens, dtype=torch.long)
@@ -245,7 +263,7 @@ def forward(config: dict, weights: Dict[str, torch.Tensor], tokens, dtype=torch.
     latents = {}
     for i, layer in enumerate(config["layers"]):
         p, m = f"l{i}", layer["mixer"]
-        h = r16(rms_norm(x, w[p + ".norm1"], eps, True))
+        h = rms_norm(x, w[p + ".norm1"], eps, True)
         if layer["type"] == "gla":
             y = gla_mixer(h, w, p + ".mix", dict(m, eps=eps))
         elif layer["type"] == "parallel":
@@ -262,7 +280,7 @@ def forward(config: dict, weights: Dict[str, torch.Tensor], tokens, dtype=torch.
             raise ValueError(layer["type"])
         mlp = layer.get("mlp")
         if mlp is not None:
-            h2 = r16(rms_norm(x, w[p + ".norm2"], eps, True))
+            h2 = rms_norm(x, w[p + ".norm2"], eps, True)
             if mlp["kind"] == "dense":
                 y = y + gated_ff(h2, w[p + ".mlp.gate"], w[p + ".mlp.up"], w[p + ".mlp.down"])
             else:
@@ -270,7 +288,7 @@ def forward(config: dict, weights: Dict[str, torch.Tensor], tokens, dtype=torch.
         x = x + y
         if layers_out is not None:
             layers_out.append(x.clone())
-    return r16(rms_norm(x, w["final.norm"], eps, True)) @ w["embed"].T
+    return lin(rms_norm(x, w["final.norm"], eps, True), w["embed"])
 
 
 def greedy(config: dict, weights, prompt, new_tokens: int, dtype=torch.float64):

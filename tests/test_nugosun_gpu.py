@@ -106,7 +106,7 @@ def runner_of(cfg, sd, dtype, page, tokens, live=4, graphs=False):
 def plain_logits(cj, sd, reqs, dtype):
     """{request: (logits, bar of every position)} of the plain implementation.  In 32-bit the bar is TOL.  In bfloat16 a
     position may be ill-conditioned (a head's output normed when its query barely meets its key, a router's close call):
-    how far rounding the sublayers' inputs alone moves the plain logits there, times three, is then its bar, and a
+    how far rounding the rows that enter every product alone moves the plain logits there, times three, is then its bar, and a
     position at which a router's choice hangs on less than a hundredth of its logits' spread is not compared.  Such positions must be few, or the test
     says nothing."""
     out = {}
@@ -196,16 +196,18 @@ def _steps_of(seqs, lens_by_step):
 @pytest.mark.parametrize("H,K,V,share", [(2, 32, 16, 1), (3, 12, 20, 1), (1, 128, 24, 1), (4, 48, 40, 2), (2, 200, 8, 2),
                                          (1, 8, 130, 1)])
 @pytest.mark.parametrize("mode", ["gate", "step", "log"])
-def test_recurrence_steps_slots_and_a_far_key(ops, H, K, V, share, mode):
+@pytest.mark.parametrize("long", [150, 600])
+def test_recurrence_steps_slots_and_a_far_key(ops, H, K, V, share, mode, long):
     """The recurrence through three steps (a long portion, short portions, one token each), slots out of order, other
     slots poisoned, state behind other elements of the slot, against the plain recurrence over the whole sequences.
     In the first request one key far back is planted with a query aimed at it under a slow decay: its value must
-    arrive at the last token."""
+    arrive at the last token.  A portion of 600 tokens is walked as segments side by side (ragged last segment) beside
+    short portions that are not."""
     if mode != "step" and share != 1:
         pytest.skip("shared q and k go with the per-head decay")
     dev = "cuda"
     g = torch.Generator().manual_seed(H * K + V)
-    cuts = [[150, 3, 1], [2, 9, 1], [1, 1, 1]]
+    cuts = [[long, 3, 1], [2, 9, 1], [1, 1, 1]]
     total = [sum(c[i] for c in cuts) for i in range(3)]
     G = H // share
     off = 7                                                  # the state does not start at the slot's first element
@@ -273,7 +275,7 @@ def test_recurrence_steps_slots_and_a_far_key(ops, H, K, V, share, mode):
     for i in range(len(seqs)):
         scale = float(want[i].abs().max())
         err = float((torch.cat(got[i]) - want[i]).abs().max()) / scale
-        assert err < 2e-5, f"request {i} off by {err:.3g}"
+        assert err < (2e-5 if long <= 256 else 5e-5), f"request {i} off by {err:.3g}"
     if mode != "step":                                       # (a slow decay there means a small step, which also scales k)
         assert float(want[0][-1, :V].abs().max()) > 100.0    # the far key's value dominates the last output of head 0
     assert torch.isnan(state[1]).all() and torch.isnan(state[4]).all()          # nobody's slots were left alone
@@ -670,12 +672,11 @@ def test_long_decoding_through_graph_replay(dtype):
     sd = weights(cfg)
     rng = random.Random(4)
     reqs = {r: [rng.randrange(cfg.vocab_size) for _ in range(n + 300)] for r, n in (("r0", 21), ("r1", 3))}
-    want = {r: P.forward(cfg.to_json_dict(), sd, t) for r, t in reqs.items()}
+    want = plain_logits(cfg.to_json_dict(), sd, reqs, dtype)
     steps = [([("r0", 0, 21), ("r1", 0, 3)], [])]
     steps += [([("r0", 21 + i, 1), ("r1", 3 + i, 1)], ["r0", "r1"] if i == 299 else []) for i in range(300)]
     r = runner_of(cfg, sd, dtype, 16, 2 * 336, live=2, graphs=True)
     got = run_trace(r, reqs, steps, poison=True)
     assert any(st["graphs"] for st in r._graphs.values()), "the decode steps were not replayed as graphs"
     for q in reqs:
-        bad = first_bad(got[q], want[q], TOL[dtype])
-        assert bad is None, f"{dtype}: request {q} token {bad[0]} off by {bad[1]:.3g}"
+        assert_within(got[q], want[q], f"{dtype}: request {q}")

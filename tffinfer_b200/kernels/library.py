@@ -1169,7 +1169,9 @@ class CudaKernels:
         projection's accumulators or tensors of their own; ``share`` heads use one q and one k.  ``mode``: "log" (dec =
         ln a per key channel), "gate" (a = sigmoid(dec + dec_bias)^inv_tau per key channel), "step" (dt = softplus(dec +
         dec_bias) per head, a = exp(-exp(rate_log) dt), k times dt).  ``state`` [slots, n] float32: a request's heads lie
-        at elements state_off .. of its slot.  out float32 [T, H*V]."""
+        at elements state_off .. of its slot.  out float32 [T, H*V].  Two kernels: the decay factors of all tokens, once,
+        then the walk over the tokens; portions of more than 256 tokens are walked as segments side by side, which a scan
+        over the segments' states and a kernel that adds what every token still lacks join (two kernels more)."""
         (qt, q0), (kt, k0), (vt, vo), (dt, d0) = q, k, v, dec
         self._need_cuda(qt, kt, vt, dt, state, out, dec_bias, rate_log, skip)
         for t in (qt, kt, vt, dt, state, out):
@@ -1181,14 +1183,22 @@ class CudaKernels:
         assert d0 + (H if m == 2 else H * K) <= dt.shape[1]
         for t, n in ((dec_bias, H if m == 2 else H * K), (rate_log, H), (skip, H)):
             assert t is None or (t.dtype == torch.float32 and t.numel() == n)
+        T = qt.shape[0]
+        self.lib.tff_linear_recurrence_workspace.restype = ctypes.c_longlong
+        need = int(self.lib.tff_linear_recurrence_workspace(_c_int(T), _c_int(batch.num_requests), _c_int(batch.max_q_len),
+                                                            _c_int(H), _c_int(K), _c_int(V), _c_int(m)))
+        factors = torch.empty(need, dtype=torch.float32, device=qt.device)
+        segmented = batch.max_q_len > self.RECURRENCE_SEGMENT
         self._check(self.lib.tff_linear_recurrence(
             _ptr(qt), _c_int(qt.shape[1]), _c_int(q0), _ptr(kt), _c_int(kt.shape[1]), _c_int(k0), _ptr(vt),
             _c_int(vt.shape[1]), _c_int(vo), _ptr(dt), _c_int(dt.shape[1]), _c_int(d0), _ptr(dec_bias), _ptr(rate_log),
             _ptr(skip), _c_int(m), _c_float(inv_tau), _c_float(q_scale), _ptr(state), ctypes.c_longlong(state.shape[1]),
             ctypes.c_longlong(state_off), _ptr(batch.q_start), _ptr(batch.pos_start), _ptr(batch.slots), _ptr(out),
-            _c_int(out.shape[1]), _c_int(batch.num_requests), _c_int(H), _c_int(K), _c_int(V), _c_int(share),
-            self._stream()), "linear_recurrence")
-        self.launches += 1
+            _c_int(out.shape[1]), _ptr(factors), _c_int(T), _c_int(batch.num_requests), _c_int(batch.max_q_len), _c_int(H),
+            _c_int(K), _c_int(V), _c_int(share), self._stream()), "linear_recurrence")
+        self.launches += 4 if segmented else 2
+
+    RECURRENCE_SEGMENT = 256      # portions longer than this run as segments side by side, joined by a scan (the kernel's constant)
 
     def gated_norm(self, o, group: int, gate, gate_off: int, weight, eps: float, gate_first: bool, out, out_off: int = 0,
                    out_scale: float = 1.0, clear_cols=None, last_reader: bool = False) -> None:
@@ -1210,7 +1220,7 @@ class CudaKernels:
             self._stream()), "gated_norm")
         if clear and last_reader:
             self._acc_zero[gate.data_ptr()] = True
-        self.launches += 1
+        self.launches += 2 if clear and hi > lo else 1
 
     def causal_conv(self, proj, col0: int, channels: int, weight, bias, activation: str, state, state_off: int, batch,
                     out, update_state: bool = False) -> bool:
