@@ -164,7 +164,6 @@ linear_recurrence_kernel(RecArgs a) {
                 if (v0 + c < V) vs[i] = __ldcg(vp + (size_t)(t0 + base + tt) * a.v_ld + c);
             }
         }
-        float* vs = buf + vec * TB * RW;
         cp_async_commit();
     };
     // Copies of 16 bytes go past the first-level cache.  Smaller ones do not, and a block that became resident before
@@ -288,11 +287,15 @@ segment_scan_kernel(RecArgs a) {
     a.state[(size_t)a.slots[b] * a.slot_stride + a.state_off + (size_t)head * K * V + e] = E;
 }
 
+constexpr int APPLY_TOKENS = 8;      // most tokens staged at a time by the apply kernel
+
 template <int KPT>
 __global__ void __launch_bounds__(REC_THREADS)
 segment_apply_kernel(RecArgs a, int tokens_a_block) {
+    extern __shared__ __align__(16) float rec_smem[];       // [TB][KS * (KPT + REC_PAD)]: q_t * P_t, laid out as q is staged above
     pdl_launch_dependents();
     const int KS = a.KS, cpw = 32 / KS, VS = REC_THREADS / KS;
+    const int KK = KS * KPT, RW = KS * (KPT + REC_PAD);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int vc = warp * cpw + lane % cpw, ks = lane / cpw;
     const int per_seg = (a.seg_len + tokens_a_block - 1) / tokens_a_block;
@@ -315,24 +318,59 @@ segment_apply_kernel(RecArgs a, int tokens_a_block) {
         const int r = ks * KPT + j;
         S[j] = (active && r < K) ? E[(size_t)r * V + vcol] : 0.f;
     }
-    const float* qp = a.q + a.q_off + grp * K + ks * KPT;
-    const float* pp = a.scalar ? a.seg_prod + head : a.seg_prod + head * K + ks * KPT;
+    const float* qp = a.q + a.q_off + grp * K;
+    const float* pp = a.scalar ? a.seg_prod + head : a.seg_prod + head * K;
     const int p_ld = a.scalar ? a.H : a.H * K;
-    for (int i = 0; i < n; ++i) {
-        const size_t t = (size_t)t_req + first + i;
-        float acc = 0.f;
-        if (a.scalar) {
+    const int TB = a.TB;                                    // tokens a batch: a thread stages at most eight products
+    float rq[APPLY_TOKENS], rp[APPLY_TOKENS];
+    auto fetch = [&](int base) {                            // q and P of the batch at ``base``: loads in flight together
+        const int nb = min(TB, n - base);
 #pragma unroll
-            for (int j = 0; j < KPT; ++j)
-                if (ks * KPT + j < K) acc = fmaf(S[j], qp[t * a.q_ld + j], acc);
-            acc *= pp[t * p_ld];
-        } else {
-#pragma unroll
-            for (int j = 0; j < KPT; ++j)
-                if (ks * KPT + j < K) acc = fmaf(S[j], qp[t * a.q_ld + j] * pp[t * p_ld + j], acc);
+        for (int j = 0; j < APPLY_TOKENS; ++j) {
+            const int i = tid + j * REC_THREADS;
+            const int tt = i >> a.kk_shift, r = i & (KK - 1);
+            const bool on = tt < nb && r < K;
+            const size_t t = (size_t)t_req + first + base + (on ? tt : 0);
+            rq[j] = on ? qp[t * a.q_ld + r] : 0.f;
+            rp[j] = on ? pp[t * p_ld + (a.scalar ? 0 : r)] : 0.f;
         }
-        for (int o = cpw; o < 32; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-        if (ks == 0 && active) a.out[t * a.out_ld + head * V + vcol] += acc * a.q_scale;
+    };
+    fetch(0);
+    for (int base = 0; base < n; base += TB) {
+        const int nb = min(TB, n - base);
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < APPLY_TOKENS; ++j) {
+            const int i = tid + j * REC_THREADS;
+            const int tt = i >> a.kk_shift, r = i & (KK - 1);
+            if (tt < TB) rec_smem[tt * RW + (r / KPT) * (KPT + REC_PAD) + r % KPT] = rq[j] * rp[j];
+        }
+        __syncthreads();
+        if (base + TB < n) fetch(base + TB);                // in flight while this batch is worked on
+        float acc[APPLY_TOKENS];
+#pragma unroll
+        for (int tt = 0; tt < APPLY_TOKENS; ++tt) {
+            float a0 = 0.f, a1 = 0.f;
+            if (tt < nb) {
+                const float4* q4 = reinterpret_cast<const float4*>(rec_smem + tt * RW + ks * (KPT + REC_PAD));
+#pragma unroll
+                for (int j = 0; j < KPT / 4; ++j) {
+                    const float4 qv = q4[j];
+                    a0 = fmaf(S[4 * j + 0], qv.x, a0); a1 = fmaf(S[4 * j + 1], qv.y, a1);
+                    a0 = fmaf(S[4 * j + 2], qv.z, a0); a1 = fmaf(S[4 * j + 3], qv.w, a1);
+                }
+            }
+            acc[tt] = a0 + a1;
+        }
+        for (int o = cpw; o < 32; o <<= 1) {
+#pragma unroll
+            for (int tt = 0; tt < APPLY_TOKENS; ++tt) acc[tt] += __shfl_xor_sync(0xffffffffu, acc[tt], o);
+        }
+        if (ks == 0 && active) {
+#pragma unroll
+            for (int tt = 0; tt < APPLY_TOKENS; ++tt)
+                if (tt < nb) a.out[((size_t)t_req + first + base + tt) * a.out_ld + head * V + vcol] += acc[tt] * a.q_scale;
+        }
     }
 }
 
@@ -416,7 +454,7 @@ TFF_API int tff_linear_recurrence(
     if (st != TFF_OK) return st;
     // Rows a thread (8, 16 or 32) against lanes a column (KS): few rows a thread make more blocks (a block owns 128 / KS
     // columns of a head), which a step of few requests and heads needs; many rows a thread read the state in longer runs.
-    // The widest that still gives every SM two blocks is taken, the narrowest that K allows otherwise.
+    // The widest that still gives every SM four blocks is taken, the narrowest that K allows otherwise.
     int sms = 0, dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -428,7 +466,7 @@ TFF_API int tff_linear_recurrence(
         if (ks > 32) break;
         KPT = kpt; KS = ks;
         const long long blocks = (long long)((V + REC_THREADS / ks - 1) / (REC_THREADS / ks)) * H * num_requests * nseg;
-        if (blocks >= 2LL * sms) break;
+        if (blocks >= 4LL * sms) break;
     }
     if (KPT == 0) return TFF_ERR_UNSUPPORTED;
     RecArgs a;
@@ -451,6 +489,7 @@ TFF_API int tff_linear_recurrence(
               k_off % 4 == 0 && v_off % 4 == 0 && on16(q) && on16(k) && on16(v) && on16(factors)) ? 1 : 0;
     const size_t smem = 2 * (size_t)a.TB * ((a.scalar ? 2 : 3) * KS * (KPT + REC_PAD) + VS + 4) * sizeof(float);
     dim3 grid((V + VS - 1) / VS, H, num_requests * nseg);
+    const size_t asmem = (size_t)a.TB * KS * (KPT + REC_PAD) * sizeof(float);
     const int apply_tokens = 64;                            // tokens a block of the apply kernel adds to
     dim3 agrid((V + VS - 1) / VS, H, num_requests * (nseg - 1) * ((REC_SEGMENT + apply_tokens - 1) / apply_tokens));
 #define TFF_REC(N)                                                                                                   \
@@ -461,7 +500,9 @@ TFF_API int tff_linear_recurrence(
         if (st != TFF_OK || nseg == 1) return st;                                                                    \
         st = tff_launch_pdl(segment_scan_kernel, dim3((K * V + 255) / 256, H, num_requests), dim3(256), 0, stream, a); \
         if (st != TFF_OK) return st;                                                                                 \
-        return tff_launch_pdl(segment_apply_kernel<N>, agrid, dim3(REC_THREADS), 0, stream, a, apply_tokens);        \
+        if (asmem > 48 * 1024)                                                                                       \
+            cudaFuncSetAttribute(segment_apply_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)asmem);  \
+        return tff_launch_pdl(segment_apply_kernel<N>, agrid, dim3(REC_THREADS), asmem, stream, a, apply_tokens);    \
     } while (0)
     if (KPT == 8) TFF_REC(8);
     if (KPT == 16) TFF_REC(16);
