@@ -781,7 +781,7 @@ def nugosun_engine(size: str, max_live: int, cache_tokens: int, graphs: bool, st
         mlp = moe if i % 2 else dense
         if kind == "parallel":
             layers.append(NugosunLayer("parallel", left=NugosunAttention(
-                LH, LG, LD, LD, LD ** -0.5 * 4.0, 50.0, CH, RotaryConfig(2.5e5, LD // 2, (8.0, 1024.0, 32.0, 1.0))),
+                LH, LG, LD, LD, LD ** -0.5 * 4.0, 30.0, CH, RotaryConfig(1e6, LD // 2, (4.0, 4096.0, 16.0, 2.0))),
                 right=NugosunStateSpace(SH, SP, SN, 1, 4, 1), left_scale=0.8, right_scale=0.9, mlp=mlp))
         elif kind == "latent":
             layers.append(NugosunLayer("latent_attention", latent=NugosunLatent(

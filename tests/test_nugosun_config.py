@@ -120,7 +120,7 @@ def test_a_size_that_only_the_file_gives():
 
 def test_package_frequencies_equal_the_plain_ones():
     from tffinfer_b200.parts.position import scaled_frequencies
-    for rot in ({"base": 250000.0, "dims": 16, "scaling": {"factor": 8.0, "original": 1024, "fast": 32.0, "slow": 1.0}},
+    for rot in ({"base": 70000.0, "dims": 24, "scaling": {"factor": 6.0, "original": 512, "fast": 24.0, "slow": 0.5}},
                 {"base": 1e4, "dims": 64, "scaling": {"factor": 4.0, "original": 64.0, "fast": 16.0, "slow": 2.0}},
                 {"base": 5e5, "dims": 6}):
         sc = rot.get("scaling")

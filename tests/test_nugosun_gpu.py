@@ -71,7 +71,7 @@ def config(name: str) -> NugosunConfig:
         return NugosunConfig("Nugosun", vocab_size=264, hidden_size=64, embed_scale=3.0, norm_eps=1e-6, layers=layers)
     if name == "d":      # blocks of 64 over pages of 32, chains of borrowed vectors, a gla layer first and last, wide state
         moe = NugosunMlp("moe", 32, 12, 3)
-        rot = RotaryConfig(2.5e5, 8, (8.0, 128.0, 32.0, 1.0))
+        rot = RotaryConfig(3e5, 8, (6.0, 128.0, 24.0, 0.5))
         layers = (gla(2, 128, 24, 16.0, 32, mlp=moe), lat(2, 24, 8, 40, 32, 56, mlp=moe),
                   par(8, 8, 16, 16, 64, 0.4, 20.0, rot, 2, 64, 80, conv=5, parts=4, mlp=moe),
                   lat(2, 24, 8, 40, 32, 56, kv_from=1, mlp=moe), lat(4, 8, 8, 8, 8, 56, mlp=NugosunMlp("dense", 40)),
@@ -611,7 +611,7 @@ def draw(seed: int):
     a_heads = rng.choice([1, 2, 4, 6])
     a_kv = rng.choice([h for h in (1, 2, 3, 4, 6) if a_heads % h == 0])
     a_dim = rng.choice([16, 32, 64, 48])
-    a_rot = rng.choice([None, RotaryConfig(rng.choice([1e4, 2.5e5]), rng.choice([4, 8, a_dim])),
+    a_rot = rng.choice([None, RotaryConfig(rng.choice([1e4, 3e5]), rng.choice([4, 8, a_dim])),
                         RotaryConfig(1e4, rng.choice([8, a_dim]), (rng.choice([2.0, 8.0]), 256.0, 32.0, 1.0))])
     s_heads = rng.choice([1, 2, 4, 6])
     s_groups = rng.choice([h for h in (1, 2, 3) if s_heads % h == 0])

@@ -483,6 +483,7 @@ TFF_API int tff_linear_recurrence(
     while ((1 << a.kk_shift) < KK) ++a.kk_shift;
     a.TB = 1024 / KK;                                       // a buffer holds at most 1024 rows of a staged vector
     if (a.TB > REC_TOKENS) a.TB = REC_TOKENS;
+    if (max_q_len > 0 && a.TB > max_q_len) a.TB = max_q_len;       // steps of single tokens: buffers of one token
     const int VS = REC_THREADS / KS;
     auto on16 = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
     a.wide = (K % 4 == 0 && V % 4 == 0 && VS % 4 == 0 && q_ld % 4 == 0 && k_ld % 4 == 0 && v_ld % 4 == 0 && q_off % 4 == 0 &&
