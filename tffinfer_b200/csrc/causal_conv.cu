@@ -36,15 +36,15 @@ causal_conv_kernel(const float* __restrict__ proj, int ld, int col0, int C, cons
     for (int j = 0; j < taps; ++j) {
         const int back = taps - 1 - j;                      // how many tokens before this one
         if (back > pos) continue;                           // ahead of the sequence's start
-        const float u = back <= i_in ? proj[(size_t)(t - back) * ld + col0 + c]
-                                     : st[(size_t)(taps - 1 - (back - i_in)) * C + c];
+        const float u = __ldcg(back <= i_in ? proj + (size_t)(t - back) * ld + col0 + c       // past the first-level cache:
+                                            : st + (size_t)(taps - 1 - (back - i_in)) * C + c);   // kernels ahead wrote these
         y = fmaf(wc[j], u, y);
     }
     if (act == 1) y = y / (1.f + expf(-y));
     out[(size_t)t * C + c] = y;
     if (update_state && taps > 1) {                         // the request's one token: its rows move up by one
-        for (int i = 0; i + 2 < taps; ++i) st[(size_t)i * C + c] = st[(size_t)(i + 1) * C + c];
-        st[(size_t)(taps - 2) * C + c] = proj[(size_t)t * ld + col0 + c];
+        for (int i = 0; i + 2 < taps; ++i) st[(size_t)i * C + c] = __ldcg(st + (size_t)(i + 1) * C + c);
+        st[(size_t)(taps - 2) * C + c] = __ldcg(proj + (size_t)t * ld + col0 + c);
     }
 }
 
@@ -62,8 +62,8 @@ causal_conv_state_kernel(const float* __restrict__ proj, int ld, int col0, int C
     pdl_wait();
     for (int i = 0; i < keep; ++i) {                        // row i of the new state: the token keep - i before the next one
         const int from_end = keep - i;                      // 1 = the portion's last token
-        st[(size_t)i * C + c] = from_end <= n ? proj[(size_t)(t0 + n - from_end) * ld + col0 + c]
-                                              : st[(size_t)(i + n) * C + c];        // an older row moves up (i + n > i)
+        st[(size_t)i * C + c] = __ldcg(from_end <= n ? proj + (size_t)(t0 + n - from_end) * ld + col0 + c
+                                                     : st + (size_t)(i + n) * C + c);       // an older row moves up (i + n > i)
     }
 }
 

@@ -35,10 +35,6 @@ static inline bool tff_pdl_enabled() {
     return v != 0;
 }
 
-// A launcher may switch the attribute off for its own launches (tff_force_plain() = 1, and back to 0 behind them): its
-// kernels then start when everything ahead of them in the stream has finished.  Each translation unit has its own switch.
-static inline int& tff_force_plain() { static int v = 0; return v; }
-
 template <typename Kern, typename... Args>
 static inline int tff_launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
     cudaLaunchConfig_t cfg = {};
@@ -47,7 +43,7 @@ static inline int tff_launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, 
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = (tff_pdl_enabled() && !tff_force_plain()) ? 1 : 0;
+    cfg.numAttrs = tff_pdl_enabled() ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kern, args...) == cudaSuccess ? TFF_OK : TFF_ERR_LAUNCH;
 }
 

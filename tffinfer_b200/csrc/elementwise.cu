@@ -159,7 +159,7 @@ __global__ void rmsnorm_pair_kernel(const float* __restrict__ x, const float* __
 #pragma unroll
         for (int k = 0; k < KEEP; ++k) {
             const int i = threadIdx.x + k * NT;
-            keep[k] = i < n4 ? x4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            keep[k] = i < n4 ? __ldcg(x4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
 #pragma unroll
         for (int k = 0; k < KEEP; ++k) {
@@ -167,7 +167,7 @@ __global__ void rmsnorm_pair_kernel(const float* __restrict__ x, const float* __
             ss = fmaf(keep[k].z, keep[k].z, ss); ss = fmaf(keep[k].w, keep[k].w, ss);
         }
         for (int i = threadIdx.x + KEEP * NT; i < n4; i += NT) {
-            const float4 v = x4[i];
+            const float4 v = __ldcg(x4 + i);
             ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
         }
         ss = block_sum<NT>(ss, red);
@@ -182,17 +182,17 @@ __global__ void rmsnorm_pair_kernel(const float* __restrict__ x, const float* __
             }
         }
         for (int i = threadIdx.x + KEEP * NT; i < n4; i += NT) {
-            const float4 v = x4[i], ga = a4[i], gb = b4[i];
+            const float4 v = __ldcg(x4 + i), ga = a4[i], gb = b4[i];
             store4<TO>(oa + 4 * i, (v.x * rs) * ga.x, (v.y * rs) * ga.y, (v.z * rs) * ga.z, (v.w * rs) * ga.w);
             store4<TO>(ob + 4 * i, (v.x * rs) * gb.x, (v.y * rs) * gb.y, (v.z * rs) * gb.z, (v.w * rs) * gb.w);
         }
         return;
     }
-    for (int i = threadIdx.x; i < dim; i += NT) { const float v = xr[i]; ss = fmaf(v, v, ss); }
+    for (int i = threadIdx.x; i < dim; i += NT) { const float v = __ldcg(xr + i); ss = fmaf(v, v, ss); }
     ss = block_sum<NT>(ss, red);
     const float rs = rsqrtf(ss / (float)dim + eps);
     for (int i = threadIdx.x; i < dim; i += NT) {
-        const float v = xr[i] * rs;
+        const float v = __ldcg(xr + i) * rs;
         oa[i] = from_f32<TO>(v * wa[i]);
         ob[i] = from_f32<TO>(v * wb[i]);
     }

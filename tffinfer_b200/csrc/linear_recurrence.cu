@@ -25,6 +25,12 @@
 // Within a batch every thread keeps its partial sums of o of all the batch's tokens; they meet across the KS lanes by
 // shuffles once a batch, eight independent chains side by side.
 //
+// Every kernel here is launched with programmatic dependent launch and reads what the kernels ahead wrote past the
+// first-level cache (16-byte asynchronous copies, ld.global.cg): a block that became resident before those kernels had
+// finished can find a line there that is older than their writes, and the wait does not drop it.  (The factors kernel
+// read its rows through that cache at first: decode steps replayed as CUDA graphs then went wrong, the same way every
+// time, and right again when it was launched plainly or read past the cache.)
+//
 // A further kernel finishes such a mixer's output: RMS norm over groups of columns with a weight, and a silu gate ahead
 // of the norm or behind it; another sets columns of an accumulator buffer back to zero.
 #include "common.cuh"
@@ -77,7 +83,7 @@ decay_factors_kernel(const float* __restrict__ dec, int dec_ld, int dec_off, con
     const float b = mode >= 1 ? dec_bias[c] : 0.f;
     const float rate = mode == 2 ? expf(rate_log[c]) : 0.f;
     pdl_wait();
-    const float raw = dec[t * dec_ld + dec_off + c];
+    const float raw = __ldcg(dec + t * dec_ld + dec_off + c);
     if (mode == 2) {
         const float dt = softplus_f(raw + b);
         fac[2 * i] = dt;
@@ -182,7 +188,7 @@ linear_recurrence_kernel(RecArgs a) {
 #pragma unroll
     for (int j = 0; j < KPT; ++j) {
         const int r = ks * KPT + j;
-        S[j] = (!fresh && active && r < K) ? st_in[(size_t)r * V + vcol] : 0.f;
+        S[j] = (!fresh && active && r < K) ? __ldcg(st_in + (size_t)r * V + vcol) : 0.f;
     }
     int which = 0;
     for (int base = 0; base < n; base += TB, which ^= 1) {
@@ -277,11 +283,11 @@ segment_scan_kernel(RecArgs a) {
     pdl_wait();
     float* U = a.seg_state + ((size_t)b * a.nseg * a.H + head) * K * V + e;
     const size_t seg_stride = (size_t)a.H * K * V;
-    float E = U[0];
+    float E = __ldcg(U);
     for (int s = 1; s < segs; ++s) {
         const size_t last = (size_t)t_req + min(n_req, (s + 1) * a.seg_len) - 1;
-        const float P = a.scalar ? a.seg_prod[last * a.H + head] : a.seg_prod[last * a.H * K + head * K + r];
-        E = fmaf(P, E, U[s * seg_stride]);
+        const float P = __ldcg(a.scalar ? a.seg_prod + last * a.H + head : a.seg_prod + last * a.H * K + head * K + r);
+        E = fmaf(P, E, __ldcg(U + s * seg_stride));
         U[s * seg_stride] = E;
     }
     a.state[(size_t)a.slots[b] * a.slot_stride + a.state_off + (size_t)head * K * V + e] = E;
@@ -316,7 +322,7 @@ segment_apply_kernel(RecArgs a, int tokens_a_block) {
 #pragma unroll
     for (int j = 0; j < KPT; ++j) {
         const int r = ks * KPT + j;
-        S[j] = (active && r < K) ? E[(size_t)r * V + vcol] : 0.f;
+        S[j] = (active && r < K) ? __ldcg(E + (size_t)r * V + vcol) : 0.f;
     }
     const float* qp = a.q + a.q_off + grp * K;
     const float* pp = a.scalar ? a.seg_prod + head : a.seg_prod + head * K;
@@ -331,8 +337,8 @@ segment_apply_kernel(RecArgs a, int tokens_a_block) {
             const int tt = i >> a.kk_shift, r = i & (KK - 1);
             const bool on = tt < nb && r < K;
             const size_t t = (size_t)t_req + first + base + (on ? tt : 0);
-            rq[j] = on ? qp[t * a.q_ld + r] : 0.f;
-            rp[j] = on ? pp[t * p_ld + (a.scalar ? 0 : r)] : 0.f;
+            rq[j] = on ? __ldcg(qp + t * a.q_ld + r) : 0.f;
+            rp[j] = on ? __ldcg(pp + t * p_ld + (a.scalar ? 0 : r)) : 0.f;
         }
     };
     fetch(0);
@@ -369,7 +375,10 @@ segment_apply_kernel(RecArgs a, int tokens_a_block) {
         if (ks == 0 && active) {
 #pragma unroll
             for (int tt = 0; tt < APPLY_TOKENS; ++tt)
-                if (tt < nb) a.out[((size_t)t_req + first + base + tt) * a.out_ld + head * V + vcol] += acc[tt] * a.q_scale;
+                if (tt < nb) {
+                    float* dst = a.out + ((size_t)t_req + first + base + tt) * a.out_ld + head * V + vcol;
+                    *dst = __ldcg(dst) + acc[tt] * a.q_scale;
+                }
         }
     }
 }
@@ -400,16 +409,16 @@ gated_norm_kernel(const float* __restrict__ o, int width, int gs, const float* _
     const int c0 = g * gs;
     float ss = 0.f;
     for (int c = c0 + first; c < c0 + gs; c += step) {
-        float u = orow[c];
-        if (gate_first) { const float z = grow[c]; u *= z / (1.f + expf(-z)); }
+        float u = __ldcg(orow + c);
+        if (gate_first) { const float z = __ldcg(grow + c); u *= z / (1.f + expf(-z)); }
         ss = fmaf(u, u, ss);
     }
     ss = WIDE ? block_sum<256>(ss, red) : warp_sum(ss);
     const float inv = rsqrtf(ss / (float)gs + eps);
     for (int c = c0 + first; c < c0 + gs; c += step) {
-        const float z = grow[c];
+        const float z = __ldcg(grow + c);
         const float sg = z / (1.f + expf(-z));
-        float y = orow[c];
+        float y = __ldcg(orow + c);
         y = gate_first ? (y * sg) * inv * w[c % wlen] : (y * inv) * w[c % wlen] * sg;
         dst[c] = from_f32<TO>(y * out_scale);
     }
@@ -441,12 +450,6 @@ TFF_API int tff_linear_recurrence(
         V <= 0 || share <= 0 || H % share || mode < 0 || mode > 2 || (mode >= 1 && !dec_bias) || (mode == 2 && !rate_log))
         return TFF_ERR_BAD_ARGUMENT;
     if (K > 1024) return TFF_ERR_UNSUPPORTED;
-    // The kernels of this launcher start only when everything ahead of them in the stream has finished (no programmatic
-    // dependent launch).  With it, decode steps replayed as CUDA graphs left wrong states behind in bfloat16 runs, the same
-    // wrong ones every time, although every access of these kernels to memory lies behind their wait; launched plainly the
-    // replays equal the kernel-by-kernel steps bit for bit.  What it costs is the overlap of a launch with the tail of
-    // the kernel ahead, a few microseconds a call.
-    struct Plain { Plain() { tff_force_plain() = 1; } ~Plain() { tff_force_plain() = 0; } } plain;
     const int per_token = mode == 2 ? H : H * K;
     const long long total = (long long)num_tokens * per_token;
     int st = tff_launch_pdl(decay_factors_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, dec, dec_ld,
