@@ -9,11 +9,12 @@
 //   0  dec holds ln a per channel                          a = exp(dec[t, h, c])
 //   1  dec holds a raw gate per channel                    a = sigmoid(dec[t, h, c] + dec_bias[h, c]) ^ inv_tau
 //   2  dec holds a raw step size per head                  dt = softplus(dec[t, h] + dec_bias[h]),
-//                                                          a = exp(-exp(rate_log[h]) * dt) on all rows, k <- dt * k
+//                                                          a = exp(-exp(rate_log[h]) * dt) on all rows, k_t v_t^T times dt
 // (modes 0 and 1 leave a [T, H * K] tensor of factors, mode 2 a [T, H, 2] tensor of (dt, a).)
 // Several heads may share one q and one k (``share`` heads a group).  All inputs are float32 rows (a product's
 // accumulators), all arithmetic is float32, and a request's tokens are walked in order, whatever the step holds
-// besides: a result does not depend on how a prompt was cut or on the batch.  The state of (slot, head) lies at
+// besides: a result does not depend on the batch, and on how a prompt was cut only in its last bits (a portion of more
+// than a segment's tokens is joined from segments, below).  The state of (slot, head) lies at
 // state + slot * slot_stride + state_off + head * K * V; a request whose first token of the step is at position 0
 // starts from zeros without reading its slot.
 //
